@@ -15,6 +15,7 @@ from typing import Any, Dict, Mapping, Type
 
 from .metulix import MetulixConfig
 from .qwen2 import ConfigError, Qwen2Config
+from .tapalix import TapalixConfig
 from .zadepel import ZadepelConfig
 
 _ARCHITECTURES: Dict[str, Type] = {}
@@ -80,3 +81,4 @@ def load_config(model_dir) -> Any:
 register_architecture("Qwen2ForCausalLM", Qwen2Config, model_type="qwen2")
 register_architecture("Metulix", MetulixConfig)
 register_architecture("Zadepel", ZadepelConfig)
+register_architecture("Tapalix", TapalixConfig)

@@ -61,11 +61,14 @@ class LayerCall:
     cache entry the mixer reads; by default a call owns the entry with its own
     position in the schedule.  `writes_cache=False` makes the mixer read that
     entry without appending to it (it must then be written by an earlier call).
+    `inlet` names a part of `ModelSpec.inlets` that changes the residual stream right
+    before this call (every time the call comes up, if the run order repeats it).
     """
 
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    inlet: Optional[int] = None      # index into ModelSpec.inlets: runs right before this call
 
 
 @dataclass(frozen=True)
@@ -80,6 +83,10 @@ class ModelSpec:
     final_norm_prefix: str
     layers: Tuple[LayerSpec, ...]
     schedule: Tuple[LayerCall, ...]
+    embedding_scale: float = 1.0           # the embedding rows are multiplied by this
+    logit_scale: float = 1.0               # logits = head(x) * logit_scale ...
+    logit_softcap: float = 0.0             # ... then cap * tanh(logits / cap) (0: no cap)
+    inlets: Tuple[Tuple[PartSpec, str], ...] = ()      # (part, tensor-name prefix) per inlet
 
     def resolved_schedule(self) -> List[Tuple[int, int, bool]]:
         """(layer, cache entry, writes) per call with defaults filled in and checked."""
@@ -93,6 +100,9 @@ class ModelSpec:
             if not 0 <= entry < len(self.schedule):
                 raise ValueError(f"schedule entry {index} names cache entry {entry} "
                                  f"outside the schedule")
+            if call.inlet is not None and not 0 <= call.inlet < len(self.inlets):
+                raise ValueError(f"schedule entry {index} names inlet {call.inlet}, "
+                                 f"the model has {len(self.inlets)}")
             if call.writes_cache:
                 if entry in written:
                     raise ValueError(f"cache entry {entry} is written twice "

@@ -50,6 +50,10 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     # attention with a scale per head and keys and values of different widths, attention over a
     # cache of latent rows
     "mixers": ("sandwich_norm.cu", "mingru.cu", "scaled_attention.cu", "latent_attention.cu"),
+    # decoders whose sublayers share one norm: layer norm with gain and bias over a sum of pending
+    # outputs, the residual stream beside the embedding output, capped logits, a sigmoid gate; and a
+    # feed-forward of routed experts
+    "routed": ("parallel_norm.cu", "routed.cu"),
 }
 # specialisations compiled by build_all() beside the default form of every library
 DEFAULT_SPECIALISATIONS = {"attn_mma": [("-DHEAD_DIM=128",)],

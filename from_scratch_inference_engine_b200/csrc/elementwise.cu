@@ -12,20 +12,20 @@ namespace fsie {
 // the device-side guard the reference kernel lacks, src/cuda/device.cu:41-50).
 template <typename T>
 __global__ void embed_gather_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                    float* __restrict__ out, int hidden, int vocab, int* error) {
+                                    float* __restrict__ out, int hidden, int vocab, float scale, int* error) {
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
     if (!ok && threadIdx.x == 0) atomicExch(error, 1);
     const T* row = table + (size_t)(ok ? id : 0) * hidden;
     float* dst = out + (size_t)t * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(row[c]) : 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = ok ? to_float(row[c]) * scale : 0.f;
 }
 
 // the same, 8 elements per thread (hidden a multiple of 8)
 template <typename T>
 __global__ void embed_gather_vec_kernel(const int* __restrict__ ids, const T* __restrict__ table,
-                                        float* __restrict__ out, int hidden, int vocab, int* error) {
+                                        float* __restrict__ out, int hidden, int vocab, float scale, int* error) {
     grid_dependency_wait();
     grid_dependents_go();
     const int t = blockIdx.x;
@@ -37,10 +37,8 @@ __global__ void embed_gather_vec_kernel(const int* __restrict__ ids, const T* __
     for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
         float v[8];
         load8(row + c, v);
-        if (!ok) {
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = 0.f;
-        }
+        for (int i = 0; i < 8; ++i) v[i] = ok ? v[i] * scale : 0.f;
         store8(dst + c, v);
     }
 }
@@ -344,19 +342,19 @@ using namespace fsie;
 extern "C" {
 
 int fsie_embed_gather(const int* ids, const void* table, float* out, int tokens, int hidden,
-                      int vocab, int dtype, int* error, cudaStream_t stream) {
+                      int vocab, float scale, int dtype, int* error, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (hidden % 8 == 0) {
         const int threads = hidden / 8 >= 256 ? 256 : (hidden / 8 >= 128 ? 128 : 64);
         if (dtype == DTYPE_F32)
-            return launch_dependent(embed_gather_vec_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, error);
-        return launch_dependent(embed_gather_vec_kernel<bf16>, tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, error);
+            return launch_dependent(embed_gather_vec_kernel<float>, tokens, threads, 0, stream, ids, (const float*)table, out, hidden, vocab, scale, error);
+        return launch_dependent(embed_gather_vec_kernel<bf16>, tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, vocab, scale, error);
     }
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == DTYPE_F32)
-        embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, error);
+        embed_gather_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, vocab, scale, error);
     else
-        embed_gather_kernel<bf16><<<tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, error);
+        embed_gather_kernel<bf16><<<tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, vocab, scale, error);
     return FSIE_LAUNCH_CHECK();
 }
 

@@ -6,7 +6,8 @@
 //
 //   latent_prep    proj[t] = [ q: heads x (dim | rope) | lat: rank | kr: rope ]
 //                  c  = lat / sqrt(mean(lat^2) + eps) * gain          -> cache row columns [0, rank)
-//                  kr rotated (pairs 2i, 2i + 1 of the leading rotary_dim) -> columns [rank, rank + rope)
+//                  kr rotated (pairs 2i, 2i + 1 of the leading rotary_dim, or - `half_pairs` - pairs
+//                  i, i + rotary_dim / 2)                              -> columns [rank, rank + rope)
 //                  each head's rope part of q, rotated the same way     -> qa[t, h, rank ...]
 //   head_product   out[t, h, :] = W[h] x[t, h, :]   for W [heads, n, k]: U_h^T before the attention
 //                  (x = the unrotated part of q, out = qa[t, h, 0 .. rank)), V_h after it.
@@ -23,7 +24,7 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int ld, const int
                                    const int* __restrict__ slot_of, T* __restrict__ pages,
                                    long long page_stride, int page_size, const float* __restrict__ gain,
                                    float eps, T* __restrict__ qa, int heads, int dim, int rope, int rank,
-                                   int rotary_dim, int* __restrict__ error) {
+                                   int rotary_dim, int half_pairs, int* __restrict__ error) {
     __shared__ float scratch[32];
     const int t = blockIdx.x;
     grid_dependency_wait();
@@ -43,10 +44,13 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int ld, const int
         const T* src = row + h * qd + dim;
         float val = to_float(src[d]);
         if (d < rotary_dim) {
-            const int i = d >> 1;
+            // the pair's index, whether d is its second member, and where the other member sits
+            const int i = half_pairs ? (d < half ? d : d - half) : d >> 1;
+            const bool second = half_pairs ? d >= half : (d & 1);
+            const int mate = half_pairs ? (second ? d - half : d + half) : d ^ 1;
             const float c = cs[i], s = cs[half + i];
-            const float other = to_float(src[d ^ 1]);
-            val = (d & 1) ? val * c + other * s : val * c - other * s;
+            const float other = to_float(src[mate]);
+            val = second ? val * c + other * s : val * c - other * s;
         }
         qa[((size_t)t * heads + h) * row_width + rank + d] = from_float<T>(val);
     }
@@ -67,10 +71,13 @@ __global__ void latent_prep_kernel(const T* __restrict__ proj, int ld, const int
     for (int d = threadIdx.x; d < rope; d += blockDim.x) {
         float val = to_float(kr[d]);
         if (d < rotary_dim) {
-            const int i = d >> 1;
+            // the pair's index, whether d is its second member, and where the other member sits
+            const int i = half_pairs ? (d < half ? d : d - half) : d >> 1;
+            const bool second = half_pairs ? d >= half : (d & 1);
+            const int mate = half_pairs ? (second ? d - half : d + half) : d ^ 1;
             const float c = cs[i], s = cs[half + i];
-            const float other = to_float(kr[d ^ 1]);
-            val = (d & 1) ? val * c + other * s : val * c - other * s;
+            const float other = to_float(kr[mate]);
+            val = second ? val * c + other * s : val * c - other * s;
         }
         dst[rank + d] = from_float<T>(val);
     }
@@ -289,7 +296,7 @@ extern "C" {
 int fsie_latent_prep(const void* proj, int ld, const int* positions, const float* cos_sin, int table_len,
                      const int* slot_of, void* pages, long long page_stride, int page_size,
                      const float* gain, float eps, void* qa, int tokens, int heads, int dim, int rope,
-                     int rank, int rotary_dim, int dtype, int* error, cudaStream_t stream) {
+                     int rank, int rotary_dim, int half_pairs, int dtype, int* error, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (heads <= 0 || dim < 0 || rope < 0 || rank <= 0 || rotary_dim < 0 || rotary_dim > rope ||
         (rotary_dim & 1) || ld < heads * (dim + rope) + rank + rope)
@@ -298,11 +305,11 @@ int fsie_latent_prep(const void* proj, int ld, const int* positions, const float
         return launch_dependent(latent_prep_kernel<float>, dim3(tokens), dim3(256), 0, stream,
                                 (const float*)proj, ld, positions, cos_sin, table_len, slot_of, (float*)pages,
                                 page_stride, page_size, gain, eps, (float*)qa, heads, dim, rope, rank,
-                                rotary_dim, error);
+                                rotary_dim, half_pairs, error);
     return launch_dependent(latent_prep_kernel<bf16>, dim3(tokens), dim3(256), 0, stream,
                             (const bf16*)proj, ld, positions, cos_sin, table_len, slot_of, (bf16*)pages,
                             page_stride, page_size, gain, eps, (bf16*)qa, heads, dim, rope, rank,
-                            rotary_dim, error);
+                            rotary_dim, half_pairs, error);
 }
 
 // x: head h of token t at t * x_ld + h * x_head (k columns); w [heads, n, k]; out: head h of token t

@@ -80,7 +80,7 @@ def core():
     if _core is None:
         lib = build.load_library("core")
         i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
-        lib.fsie_embed_gather.argtypes = [p, p, p, i, i, i, i, p, p]
+        lib.fsie_embed_gather.argtypes = [p, p, p, i, i, i, f, i, p, p]
         lib.fsie_add_rmsnorm.argtypes = [p, p, p, i, p, p, i, i, f, i, i, p]
         lib.fsie_rope_kv_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p]
         lib.fsie_swiglu.argtypes = [p, p, ll, i, i, p]
@@ -111,8 +111,9 @@ def core():
 
 # ------------------------------------------------------------------------- embedding
 def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-                 error: torch.Tensor) -> torch.Tensor:
-    """out[t] = table[ids[t]] widened to float32; an id outside the table sets error[0]."""
+                 error: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[ids[t]] widened to float32 (times `scale`); an id outside the table sets
+    error[0]."""
     _need(ids, torch.int32, "ids")
     _need(table, None, "table")
     _need(out, torch.float32, "out")
@@ -121,7 +122,7 @@ def embed_gather(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
     if out.shape[-1] != hidden or out.numel() < tokens * hidden:
         raise KernelError("embed_gather: out is too small")
     _check(core().fsie_embed_gather(_ptr(ids), _ptr(table), _ptr(out), tokens, hidden, vocab,
-                                    _tag(table.dtype), _ptr(error), _stream()), "embed_gather")
+                                    float(scale), _tag(table.dtype), _ptr(error), _stream()), "embed_gather")
     return out
 
 
@@ -1125,7 +1126,7 @@ def mixers():
                                               p, i, p, p, i, i, i, i, i, i, i, p, p]
         lib.fsie_rotate_mix_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p,
                                               i, p, p]
-        lib.fsie_latent_prep.argtypes = [p, i, p, p, i, p, p, ll, i, p, f, p, i, i, i, i, i, i, i, p, p]
+        lib.fsie_latent_prep.argtypes = [p, i, p, p, i, p, p, ll, i, p, f, p, i, i, i, i, i, i, i, i, p, p]
         lib.fsie_head_product.argtypes = [p, ll, i, p, p, ll, i, i, i, i, i, i, p]
         for name in ("fsie_norm_add_norm", "fsie_gated_act", "fsie_mingru_scan",
                      "fsie_scaled_attention_rows", "fsie_scaled_attention", "fsie_rotate_mix_write",
@@ -1292,11 +1293,12 @@ def rotate_mix_write(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch
 def latent_prep(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
                 slot_of: torch.Tensor, pages: torch.Tensor, page_stride: int, page_size: int,
                 gain: torch.Tensor, eps: float, qa: torch.Tensor, heads: int, dim: int, rope: int,
-                rank: int, rotary_dim: int, error: torch.Tensor) -> None:
+                rank: int, rotary_dim: int, error: torch.Tensor, half_pairs: bool = False) -> None:
     """proj [tokens, heads x (dim | rope) | rank | rope]: the RMS-normed latent (gain, eps) and the
     rotated shared key part into the token's cache row [rank | rope]; every head's rotated rope
     part of q into qa [tokens, heads, rank + rope] behind the rank columns.  Rotation of pairs
-    (2i, 2i + 1) of the first rotary_dim columns of a rope part."""
+    (2i, 2i + 1) of the first rotary_dim columns of a rope part, or - `half_pairs` - of pairs
+    (i, i + rotary_dim / 2)."""
     _need(proj, None, "proj")
     _need(positions, torch.int32, "positions")
     _need(cos_sin, torch.float32, "cos_sin")
@@ -1312,7 +1314,7 @@ def latent_prep(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tens
     _check(mixers().fsie_latent_prep(_ptr(proj), ld, _ptr(positions), _ptr(cos_sin), cos_sin.shape[0],
                                      _ptr(slot_of), _ptr(pages), page_stride, page_size, _ptr(gain),
                                      float(eps), _ptr(qa), tokens, heads, dim, rope, rank, rotary_dim,
-                                     _tag(proj.dtype), _ptr(error), _stream()), "latent_prep")
+                                     int(half_pairs), _tag(proj.dtype), _ptr(error), _stream()), "latent_prep")
 
 
 def head_product(x: torch.Tensor, x_ld: int, x_head: int, weight: torch.Tensor, out: torch.Tensor,
@@ -1325,4 +1327,207 @@ def head_product(x: torch.Tensor, x_ld: int, x_head: int, weight: torch.Tensor, 
     heads, n, k = weight.shape
     _check(mixers().fsie_head_product(_ptr(x), x_ld, x_head, _ptr(weight), _ptr(out), out_ld, out_head,
                                       tokens, heads, n, k, _tag(x.dtype), _stream()), "head_product")
+    return out
+
+
+# ------------------------------------------------- one norm for two sublayers; routed experts
+_routed = None
+
+
+def routed():
+    """The library of decoders whose sublayers share one norm and whose feed-forward is a set of
+    routed experts (layer norm with gain and bias over a sum of pending outputs, the residual stream
+    beside the embedding output, a cap on the logits, a sigmoid gate; router, sorting of the
+    (token, expert) pairs, the experts' products, the weighted sum), compiled at first use."""
+    global _routed
+    if _routed is None:
+        lib = build.load_library("routed")
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_sum_layernorm.argtypes = [p, p, p, p, p, p, p, i, i, f, i, i, p]
+        lib.fsie_settle_concat.argtypes = [p, p, p, p, p, i, i, i, p]
+        lib.fsie_logit_cap.argtypes = [p, ll, f, f, p]
+        lib.fsie_sigmoid_gate.argtypes = [p, i, p, i, i, i, i, p]
+        lib.fsie_moe_tile_rows.argtypes = []
+        lib.fsie_moe_route.argtypes = [p, i, p, p, p, p, i, i, i, i, i, i, f, i, i, i, p]
+        lib.fsie_moe_align.argtypes = [p, i, i, p, p, p, p, p, p]
+        lib.fsie_moe_product.argtypes = [p, ll, p, p, ll, p, p, p, p, p, i, i, i, i, i, i, i, i, p]
+        lib.fsie_moe_combine.argtypes = [p, p, p, p, i, i, i, i, p]
+        for name in ("fsie_sum_layernorm", "fsie_settle_concat", "fsie_logit_cap", "fsie_sigmoid_gate",
+                     "fsie_moe_tile_rows", "fsie_moe_route", "fsie_moe_align", "fsie_moe_product",
+                     "fsie_moe_combine"):
+            getattr(lib, name).restype = i
+        _routed = lib
+    return _routed
+
+
+def sum_layernorm(x: torch.Tensor, deltas, gain: Optional[torch.Tensor], bias: Optional[torch.Tensor],
+                  eps: float, out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                  write_x: bool = True) -> Optional[torch.Tensor]:
+    """x (float32 residual) += d1 + d2 for the up to two pending sublayer outputs in `deltas`;
+    out = (x - mean) / sqrt(mean((x - mean)^2) + eps) * gain + bias in out's dtype.  Without `out`
+    the sum alone.  With `rows` (int32 indices) only those rows, into out[0..len(rows)), and x is
+    left untouched unless write_x."""
+    _need(x, torch.float32, "x")
+    width = x.shape[-1]
+    deltas = [d for d in (deltas or ()) if d is not None]
+    if len(deltas) > 2:
+        raise KernelError("sum_layernorm: at most two pending outputs")
+    dtype = out.dtype if out is not None else (deltas[0].dtype if deltas else None)
+    if dtype is None:
+        raise KernelError("sum_layernorm: nothing to do")
+    for d in deltas:
+        _need(d, dtype, "delta")
+        if d.shape[-1] != width or d.numel() != x.numel():
+            raise KernelError("sum_layernorm: a pending output is not of x's shape")
+    if out is not None:
+        _need(out, None, "out")
+        _need(gain, torch.float32, "gain")
+        if gain.numel() != width or (bias is not None and bias.numel() != width):
+            raise KernelError("sum_layernorm: gain or bias width differs from x")
+        if bias is not None:
+            _need(bias, torch.float32, "bias")
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        count = rows.numel()
+    else:
+        count = x.numel() // width
+    if out is not None and out.numel() < count * width:
+        raise KernelError("sum_layernorm: out is too small")
+    d1 = deltas[0] if deltas else None
+    d2 = deltas[1] if len(deltas) > 1 else None
+    _check(routed().fsie_sum_layernorm(_ptr(x), _ptr(d1), _ptr(d2), _ptr(gain), _ptr(bias), _ptr(rows),
+                                       _ptr(out), count, width, float(eps), int(write_x), _tag(dtype),
+                                       _stream()), "sum_layernorm")
+    return out
+
+
+def settle_concat(x: torch.Tensor, deltas, x0: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = [x[t] + d1[t] + d2[t] | x0[t]] in out's dtype ([tokens, 2 width]); x and x0 are
+    float32 and stay as they are."""
+    _need(x, torch.float32, "x")
+    _need(x0, torch.float32, "x0")
+    _need(out, None, "out")
+    tokens, width = x.shape
+    deltas = [d for d in (deltas or ()) if d is not None]
+    if len(deltas) > 2 or x0.shape != x.shape or out.numel() < 2 * x.numel():
+        raise KernelError("settle_concat: shapes do not fit")
+    for d in deltas:
+        _need(d, out.dtype, "delta")
+        if d.numel() != x.numel():
+            raise KernelError("settle_concat: a pending output is not of x's shape")
+    d1 = deltas[0] if deltas else None
+    d2 = deltas[1] if len(deltas) > 1 else None
+    _check(routed().fsie_settle_concat(_ptr(x), _ptr(d1), _ptr(d2), _ptr(x0), _ptr(out), tokens, width,
+                                       _tag(out.dtype), _stream()), "settle_concat")
+    return out
+
+
+def logit_cap(logits: torch.Tensor, scale: float, cap: float) -> torch.Tensor:
+    """logits <- cap * tanh(logits * scale / cap) in place (cap = 0: logits * scale)."""
+    _need(logits, torch.float32, "logits")
+    _check(routed().fsie_logit_cap(_ptr(logits), logits.numel(), float(scale), float(cap), _stream()),
+           "logit_cap")
+    return logits
+
+
+def sigmoid_gate(out: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """out[t, c] <- out[t, c] * sigmoid(gate[t, c]); `gate` may be a view of columns of a wider
+    tensor."""
+    _need(out, None, "out", contiguous=False)
+    _need(gate, out.dtype, "gate", contiguous=False)
+    tokens, width = out.shape
+    if gate.shape != out.shape or out.stride(1) != 1 or gate.stride(1) != 1:
+        raise KernelError("sigmoid_gate: shapes do not fit")
+    _check(routed().fsie_sigmoid_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), tokens, width,
+                                      _tag(out.dtype), _stream()), "sigmoid_gate")
+    return out
+
+
+def moe_tile_rows() -> int:
+    return routed().fsie_moe_tile_rows()
+
+
+def moe_route(y: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+              ids: torch.Tensor, weights: torch.Tensor, top: int, groups: int, keep: int, scale: float,
+              scores: str = "sigmoid", normalise: bool = True) -> None:
+    """Per token: s = sigmoid (or softmax) of w_router y in 32-bit; the `top` experts with the largest
+    s + correction among the `keep` best of `groups` groups (a group's score: its two largest);
+    weights s / (their sum + 1e-20) * scale.  ids int32, weights float32, both [tokens, top]."""
+    _need(y, None, "y", contiguous=False)
+    _need(w_router, torch.float32, "w_router")
+    _need(ids, torch.int32, "ids")
+    _need(weights, torch.float32, "weights")
+    tokens, width = y.shape
+    experts = w_router.shape[0]
+    if correction is not None:
+        _need(correction, torch.float32, "correction")
+    if w_router.shape[1] != width or ids.numel() < tokens * top or weights.numel() < tokens * top or \
+            y.stride(1) != 1 or scores not in ("sigmoid", "softmax"):
+        raise KernelError("moe_route: shapes do not fit")
+    _check(routed().fsie_moe_route(_ptr(y), y.stride(0), _ptr(w_router), _ptr(correction), _ptr(ids),
+                                   _ptr(weights), tokens, width, experts, int(top), int(groups), int(keep),
+                                   float(scale), int(scores == "softmax"), int(normalise), _tag(y.dtype),
+                                   _stream()), "moe_route")
+
+
+def moe_align(ids: torch.Tensor, pairs: int, experts: int, lists: torch.Tensor) -> Tuple[torch.Tensor, ...]:
+    """Sort the (token, choice) pairs by expert.  `lists` is int32 working memory of at least
+    `moe_lists_size(pairs, experts)` entries; returns its views (offsets [experts + 1], sorted [pairs],
+    tile_expert, tile_row0, meta [1])."""
+    _need(ids, torch.int32, "ids")
+    _need(lists, torch.int32, "lists")
+    tiles = pairs // moe_tile_rows() + experts
+    if lists.numel() < moe_lists_size(pairs, experts) or ids.numel() < pairs:
+        raise KernelError("moe_align: working memory is too small")
+    cut = 0
+    views = []
+    for n in (experts + 1, pairs, tiles, tiles, 1):
+        views.append(lists[cut:cut + n])
+        cut += n
+    offsets, order, tile_expert, tile_row0, meta = views
+    _check(routed().fsie_moe_align(_ptr(ids), pairs, experts, _ptr(offsets), _ptr(order), _ptr(tile_expert),
+                                   _ptr(tile_row0), _ptr(meta), _stream()), "moe_align")
+    return offsets, order, tile_expert, tile_row0, meta
+
+
+def moe_lists_size(pairs: int, experts: int) -> int:
+    return experts + 1 + pairs + 2 * (pairs // moe_tile_rows() + experts) + 1
+
+
+def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists, pairs: int, top: int,
+                gated: bool, activation: str = "silu") -> torch.Tensor:
+    """The experts' products over the sorted pairs.  gated: weight [experts, 2 n, k] (gate rows, then up
+    rows), x [tokens, k] read at pair // top, out [pairs, n] = f(gate) * up in sorted order.  Not gated:
+    weight [experts, n, k], x [pairs, k] in sorted order, out [pairs, n] at each pair's own row."""
+    _need(x, None, "x", contiguous=False)
+    _need(weight, x.dtype, "weight")
+    _need(out, x.dtype, "out")
+    offsets, order, tile_expert, tile_row0, meta = lists
+    experts, rows, k = weight.shape
+    n = rows // 2 if gated else rows
+    if x.shape[1] != k or x.stride(1) != 1 or out.shape[1] != n or out.shape[0] < pairs or \
+            (gated and rows % 2):
+        raise KernelError("moe_product: shapes do not fit")
+    _check(routed().fsie_moe_product(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0),
+                                     _ptr(offsets), _ptr(order), _ptr(tile_expert), _ptr(tile_row0),
+                                     _ptr(meta), pairs, experts, int(top), n, k, int(gated),
+                                     GATE_KINDS[activation], _tag(x.dtype), _stream()), "moe_product")
+    return out
+
+
+def moe_combine(expert_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
+                out: torch.Tensor, top: int) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * expert_out[t * top + j] (+ shared[t]), summed in 32-bit."""
+    _need(expert_out, None, "expert_out")
+    _need(weights, torch.float32, "weights")
+    _need(out, expert_out.dtype, "out")
+    tokens, width = out.shape
+    if shared is not None:
+        _need(shared, expert_out.dtype, "shared")
+        if shared.shape != out.shape:
+            raise KernelError("moe_combine: the shared expert's output is not of out's shape")
+    if expert_out.numel() < tokens * top * width or weights.numel() < tokens * top:
+        raise KernelError("moe_combine: shapes do not fit")
+    _check(routed().fsie_moe_combine(_ptr(expert_out), _ptr(weights), _ptr(shared), _ptr(out), tokens,
+                                     width, int(top), _tag(out.dtype), _stream()), "moe_combine")
     return out

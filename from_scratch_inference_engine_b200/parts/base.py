@@ -1,6 +1,6 @@
 """Interfaces of the parts a layer is put together from, and their registries.
 
-Roles: "norm", "position", "mixer", "feed_forward", "arrangement".  A part is built
+Roles: "norm", "position", "mixer", "feed_forward", "arrangement", "inlet".  A part is built
 from a `PartSpec` (kind + keyword parameters) and a tensor-name prefix; it declares
 the tensors it needs, takes them at `bind`, and runs on a `StepContext`.  No part
 knows which model it is in: sizes and constants come from the parameters, the batch
@@ -15,6 +15,9 @@ and the cache come from the context.
     class Arrangement:    forward(ctx, x, delta, cache) -> delta'
                           (x is the float32 residual stream, updated in place; delta is
                           the output of the previous sublayer not yet added to x)
+    class Inlet:          forward(ctx, x, delta, x0) -> x'
+                          (runs between two calls of the run order; x0 is the embedding output of
+                          the step's tokens; nothing is left pending behind it)
 """
 
 from __future__ import annotations
@@ -28,7 +31,7 @@ from ..cache.manager import CacheNeed
 from ..config.spec import PartSpec
 from ..weights.tensor_spec import TensorSpec
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement")
+ROLES = ("norm", "position", "mixer", "feed_forward", "arrangement", "inlet")
 _REGISTRY: Dict[str, Dict[str, type]] = {role: {} for role in ROLES}
 
 

@@ -10,7 +10,7 @@ from ..config.spec import LayerSpec
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import LayerCache, Part, build_part, register_part
-from .norm import LayerNorm, NormedDelta, RMSNorm
+from .norm import LayerNorm, NormedDelta, PendingSum, RMSNorm
 
 
 @register_part("arrangement", "prenorm")
@@ -196,3 +196,49 @@ class SandwichBlock(Part):
             return mixed
         y = self.feed_forward_norm.forward(x, mixed, tag="sandwich.feed_forward_in")
         return self.feed_forward_out_norm.pending(self.feed_forward.forward(ctx, y))
+
+
+@register_part("arrangement", "parallel")
+class ParallelBlock(Part):
+    """y = norm(x); x += mixer(y) + feed_forward(y): one norm, and both sublayers read its output.
+    A layer may have no feed-forward.
+
+    The residual stream `x` is float32 and is updated in place.  The two outputs are not added at
+    once: they are handed on as a `PendingSum`, and the kernel of the norm that runs next (the next
+    layer's, or the model's final norm on the wanted rows only) adds both to x in 32-bit and norms
+    the sum in one pass over the row.
+    """
+
+    def __init__(self, prefix: str, layer: LayerSpec):
+        self.prefix = prefix
+        self.norm = build_part("norm", layer.mixer_norm, prefix + layer.mixer_norm_name)
+        if not isinstance(self.norm, LayerNorm):
+            raise TypeError("the parallel arrangement takes a norm that adds a pending sum (layernorm)")
+        self.mixer = build_part("mixer", layer.mixer, prefix + layer.mixer_name)
+        self.feed_forward = None
+        if layer.feed_forward is not None:
+            self.feed_forward = build_part("feed_forward", layer.feed_forward,
+                                           prefix + layer.feed_forward_name)
+
+    def parts(self):
+        return [part for part in (self.norm, self.mixer, self.feed_forward) if part is not None]
+
+    @property
+    def capturable(self) -> bool:
+        return all(part.capturable for part in self.parts())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [spec for part in self.parts() for spec in part.tensor_specs()]
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        for part in self.parts():
+            part.bind(tensors, runtime)
+
+    def forward(self, ctx, x: torch.Tensor, delta, cache: LayerCache) -> PendingSum:
+        ctx.residual_copy = None
+        y = self.norm.forward(x, delta, write_x=True, tag="parallel.in")
+        mixed = self.mixer.forward(ctx, y, cache)
+        if self.feed_forward is None:
+            return PendingSum((mixed,))
+        return PendingSum((mixed, self.feed_forward.forward(ctx, y)))

@@ -21,8 +21,11 @@ class LatentAttention(Mixer):
     c = rms_norm(lat) * gain is the latent, kr a single rotated key vector that every head uses.  Head h
     has keys [U_h c | kr] and values V_h c (W_uk = U, W_uv = V stacked head by head); scores
     (q . k) * scale over the keys j in (i - window, i] (all j <= i without a window); softmax;
-    output projection on the concatenated heads.  Rotation by `position` (pairs 2i, 2i + 1) over
-    the first rotary_dim columns of a rope part.
+    output projection on the concatenated heads.  Rotation by `position` over the first
+    rotary_dim columns of a rope part, of the pairs that the position part names (2i with 2i + 1,
+    or i with i + rotary_dim / 2).  rope_dim = 0: no rotated part, W_dkv y is the latent alone.
+    `gate`: the concatenated heads are multiplied element by element by sigmoid(W_g y) before the
+    output projection (W_g reads the same y as the other projections and rides in their product).
 
     Only [c | kr] is cached: one row per token, read by every head as key and as value.  Keys and
     values per head are never formed: (U_h^T q_h) . c = q_h . (U_h c), so the queries take U over
@@ -34,11 +37,11 @@ class LatentAttention(Mixer):
 
     capturable = True
 
-    NAMES = {"q": "q", "dkv": "dkv", "norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o"}
+    NAMES = {"q": "q", "dkv": "dkv", "norm": "dkv.norm", "uk": "uk", "uv": "uv", "o": "o", "g": "g"}
 
     def __init__(self, prefix: str, hidden_size: int, heads: int, dim: int, rope_dim: int,
                  vdim: int, rank: int, scale: float, eps: float, position: PartSpec,
-                 window: int = 0, names: Optional[Dict[str, str]] = None):
+                 window: int = 0, names: Optional[Dict[str, str]] = None, gate: bool = False):
         self.prefix, self.hidden_size = prefix, int(hidden_size)
         self.heads, self.dim, self.rope_dim = int(heads), int(dim), int(rope_dim)
         self.vdim, self.rank = int(vdim), int(rank)
@@ -48,8 +51,11 @@ class LatentAttention(Mixer):
         self.position = build_part("position", position, prefix)
         if self.position.rotary_dim > self.rope_dim:
             raise ValueError("the rotated size exceeds the rope part")
-        if self.position.rotary_dim and getattr(self.position, "pairing", "") != "interleaved":
-            raise ValueError("latent_attention rotates interleaved pairs")
+        pairing = getattr(self.position, "pairing", "interleaved")
+        if self.position.rotary_dim and pairing not in ("interleaved", "half"):
+            raise ValueError("latent_attention rotates interleaved pairs or pairs half a rotation apart")
+        self.half_pairs = pairing == "half"
+        self.gate = bool(gate)
         self.names = dict(self.NAMES)
         self.names.update(names or {})
         self.w_in = self.w_uk_t = self.w_uv = self.w_o = self.gain = self.head_scale = None
@@ -61,7 +67,9 @@ class LatentAttention(Mixer):
                 TensorSpec(p + n["norm"], (self.rank,), role="vector", init="gain"),
                 TensorSpec(p + n["uk"], (self.heads * self.dim, self.rank)),
                 TensorSpec(p + n["uv"], (self.heads * self.vdim, self.rank)),
-                TensorSpec(p + n["o"], (h, self.heads * self.vdim))] + self.position.tensor_specs()
+                TensorSpec(p + n["o"], (h, self.heads * self.vdim))] + \
+            ([TensorSpec(p + n["g"], (self.heads * self.vdim, h))] if self.gate else []) + \
+            self.position.tensor_specs()
 
     def cache_need(self) -> Optional[CacheNeed]:
         return CacheNeed(1, self.row, self.window, 0, self.rank, values_in_keys=True)
@@ -69,7 +77,8 @@ class LatentAttention(Mixer):
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
         p, n = self.prefix, self.names
-        self.w_in = torch.cat([tensors[p + n["q"]], tensors[p + n["dkv"]]]).contiguous()
+        stacked = [tensors[p + n["q"]], tensors[p + n["dkv"]]] + ([tensors[p + n["g"]]] if self.gate else [])
+        self.w_in = torch.cat(stacked).contiguous()
         self.gain = tensors[p + n["norm"]].to(torch.float32).contiguous()
         # U_h^T [rank, dim] per head: the product that takes U over to the queries
         self.w_uk_t = tensors[p + n["uk"]].view(self.heads, self.dim, self.rank) \
@@ -90,7 +99,8 @@ class LatentAttention(Mixer):
         qa = rt.buffer("latent.q", tokens, self.heads * self.row, proj.dtype)
         ops.latent_prep(proj, ctx.positions, self.position.table, group.slot_of, cache.k_pages,
                         cache.page_stride, group.page_size, self.gain, self.eps, qa, self.heads,
-                        self.dim, self.rope_dim, self.rank, self.position.rotary_dim, ctx.error)
+                        self.dim, self.rope_dim, self.rank, self.position.rotary_dim, ctx.error,
+                        half_pairs=self.half_pairs)
         ops.head_product(proj, proj.stride(0), self.q_head, self.w_uk_t, qa, self.heads * self.row,
                          self.row, tokens)
         over_c = rt.buffer("latent.over_c", tokens, self.heads * self.rank, proj.dtype)
@@ -99,4 +109,7 @@ class LatentAttention(Mixer):
         out = rt.buffer("latent.out", tokens, self.heads * self.vdim, proj.dtype)
         ops.head_product(over_c, self.heads * self.rank, self.rank, self.w_uv, out,
                          self.heads * self.vdim, self.vdim, tokens)
+        if self.gate:
+            first = self.heads * self.q_head + self.row
+            ops.sigmoid_gate(out, proj[:, first:first + self.heads * self.vdim])
         return rt.linear(out, self.w_o, None, "latent.o")

@@ -16,7 +16,9 @@ from .base import LayerCache, StateNeed, build_part
 
 
 class DecoderModel:
-    """Embedding -> blocks in the order of `spec.schedule` -> final norm -> head.
+    """Embedding (times `embedding_scale`) -> blocks in the order of `spec.schedule`, an inlet
+    before the calls that name one -> final norm -> head, times `logit_scale`, capped by
+    `logit_softcap * tanh(. / logit_softcap)` where a cap is given.
 
     The run order is data: entry i of the schedule runs block `layer` on cache entry
     `cache` (its own by default).  A block named twice runs twice with the same weights;
@@ -30,6 +32,8 @@ class DecoderModel:
         self.blocks = [build_part("arrangement",
                                   _arrangement_spec(layer), layer.prefix) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        self.inlets = [build_part("inlet", part, prefix) for part, prefix in spec.inlets]
+        self.inlet_before = [call.inlet for call in spec.schedule]
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.runtime = None
@@ -46,6 +50,8 @@ class DecoderModel:
             specs.append(TensorSpec("lm_head.weight", shape, optional=True,
                                     same_as=spec.embedding_name))
         specs += self.final_norm.tensor_specs()
+        for inlet in self.inlets:
+            specs += inlet.tensor_specs()
         for block in self.blocks:
             specs += block.tensor_specs()
         return specs
@@ -68,6 +74,8 @@ class DecoderModel:
                      if self.spec.head_name is not None else self.embedding)
         runtime.prepare_weight(self.head)
         self.final_norm.bind(placed, runtime)
+        for inlet in self.inlets:
+            inlet.bind(placed, runtime)
         for block in self.blocks:
             block.bind(placed, runtime)
 
@@ -75,7 +83,8 @@ class DecoderModel:
     @property
     def capturable(self) -> bool:
         """Whether a step launches the same kernels whatever the data (every part says so)."""
-        return self.final_norm.capturable and all(block.capturable for block in self.blocks)
+        return self.final_norm.capturable and all(block.capturable for block in self.blocks) \
+            and all(inlet.capturable for inlet in self.inlets)
 
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """Need of each cache entry (index = position in the run order); None where the
@@ -108,17 +117,28 @@ class DecoderModel:
         rt = self.runtime
         hidden = self.spec.hidden_size
         x = rt.buffer("model.residual", ctx.num_tokens, hidden, torch.float32)
-        ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error)
+        scale = self.spec.embedding_scale
+        ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error, scale)
+        x0 = None
+        if self.inlets:                   # the embedding output, for the inlets that read it
+            x0 = rt.buffer("model.embedding_output", ctx.num_tokens, hidden, torch.float32)
+            ops.embed_gather(ctx.token_ids, self.embedding, x0, ctx.error, scale)
         delta = None
         ctx.residual_copy = None          # x in the compute dtype, where an arrangement keeps one
         for index, (layer, _, _) in enumerate(self.schedule):
+            if self.inlet_before[index] is not None:
+                x, delta = self.inlets[self.inlet_before[index]].forward(ctx, x, delta, x0), None
+                ctx.residual_copy = None
             delta = self.blocks[layer].forward(ctx, x, delta, caches[index])
         if want_rows is None or want_rows.numel() == 0:
             return None
         y = self.final_norm.forward(x, delta, rows=want_rows, write_x=False)
         # the logits live where the last step's lived: whoever gets them reads them (or queues
         # what reads them on this stream) before the next step runs
-        return rt.linear_f32_out(y, self.head, "model.logits")
+        logits = rt.linear_f32_out(y, self.head, "model.logits")
+        if self.spec.logit_scale != 1.0 or self.spec.logit_softcap > 0.0:
+            ops.logit_cap(logits, self.spec.logit_scale, self.spec.logit_softcap)
+        return logits
 
 
 def _arrangement_spec(layer):

@@ -23,6 +23,15 @@ class NormedDelta:
     eps: float
 
 
+@dataclass
+class PendingSum:
+    """The outputs of sublayers that read the same norm, still to be added to the residual stream
+    (x += d1 + d2): what an arrangement with one norm for both sublayers hands to the norm that
+    runs next."""
+
+    deltas: tuple
+
+
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
     """y = x * rsqrt(mean(x^2) + eps) * gain over the last axis, a plain gain (not 1 + gain),
@@ -73,39 +82,55 @@ class RMSNorm(Part):
 
 @register_part("norm", "layernorm")
 class LayerNorm(Part):
-    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * gain over the last axis: a gain and no
-    bias, statistics in 32-bit.  The tensor is `prefix + weight_name`.
+    """y = (x - mean) / sqrt(mean((x - mean)^2) + eps) * gain (+ bias) over the last axis,
+    statistics in 32-bit.  The gain is `prefix + weight_name`; with `bias_name` there is a bias,
+    the tensor `prefix + bias_name`.
 
-    Two uses: `forward` norms rows of the float32 residual stream (a model's final norm);
-    `accumulate` norms a sublayer's output and adds it into the residual stream, for
-    arrangements whose norms sit on the outputs of the sublayers.
+    Two uses: `forward` norms rows of the float32 residual stream (an arrangement's input norm, a
+    model's final norm), adding what is still pending first; `accumulate` norms a sublayer's
+    output and adds it into the residual stream, for arrangements whose norms sit on the outputs
+    of the sublayers.
     """
 
     capturable = True
 
-    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight"):
+    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight",
+                 bias_name: Optional[str] = None):
         self.prefix, self.width, self.eps = prefix, int(width), float(eps)
         self.name = prefix + weight_name
+        self.bias_name = None if bias_name is None else prefix + bias_name
         self.gain: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.width,), role="vector", init="gain")]
+        specs = [TensorSpec(self.name, (self.width,), role="vector", init="gain")]
+        if self.bias_name is not None:
+            specs.append(TensorSpec(self.bias_name, (self.width,), role="vector", init="normal"))
+        return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
         self.gain = tensors[self.name].to(torch.float32).contiguous()
+        if self.bias_name is not None:
+            self.bias = tensors[self.bias_name].to(torch.float32).contiguous()
 
-    def forward(self, x: torch.Tensor, delta: Optional[torch.Tensor] = None,
+    def forward(self, x: torch.Tensor, delta: Union[None, torch.Tensor, PendingSum] = None,
                 rows: Optional[torch.Tensor] = None, write_x: bool = False,
                 tag: Optional[str] = None) -> torch.Tensor:
-        """The normed rows of x (all, or those `rows` names) in the compute dtype."""
-        if delta is not None:
-            raise ValueError("LayerNorm.forward: no pending sublayer output is taken here")
+        """The normed rows of x (all, or those `rows` names) in the compute dtype.  What is
+        pending (`delta`: one sublayer output, or a `PendingSum` of up to two) is added to x
+        first, in 32-bit, and - with `write_x` - stays added."""
         count = x.shape[0] if rows is None else rows.numel()
         out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
-        return ops.layernorm_rows(x, self.gain, self.eps, out, rows=rows)
+        if delta is None and self.bias is None:
+            return ops.layernorm_rows(x, self.gain, self.eps, out, rows=rows)
+        deltas = delta.deltas if isinstance(delta, PendingSum) else (delta,)
+        return ops.sum_layernorm(x, deltas, self.gain, self.bias, self.eps, out, rows=rows,
+                                 write_x=write_x)
 
     def accumulate(self, x: torch.Tensor, delta: torch.Tensor,
                    copy: Optional[torch.Tensor]) -> None:
         """x += LN(delta) * gain; `copy` (compute dtype) receives the new x when given."""
+        if self.bias is not None:
+            raise ValueError("LayerNorm.accumulate takes a norm without bias")
         ops.add_layernorm(x, delta, self.gain, self.eps, copy)

@@ -21,6 +21,31 @@ def rotary_table(theta: float, rotary_dim: int, length: int) -> np.ndarray:
     return np.concatenate([np.cos(angles), np.sin(angles)], axis=1).astype(np.float32)
 
 
+def yarn_rotary_table(theta: float, rotary_dim: int, length: int, factor: float, original: float,
+                      fast: float, slow: float) -> np.ndarray:
+    """The table of `rotary_table` with YaRN's change of the frequencies and of the magnitude.
+
+    With dim(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(dim(fast)), 0),
+    hi = min(ceil(dim(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1),
+    pair i turns by position * (f_i / factor * ramp_i + f_i * (1 - ramp_i)): pairs that turn often
+    within the original length keep their frequency, slow ones are stretched by `factor`.  Cos and
+    sin are both multiplied by 0.1 ln(factor) + 1.  64-bit on the host, rounded once."""
+    import math
+    half = rotary_dim // 2
+    index = np.arange(half, dtype=np.float64)
+    inv_freq = np.power(float(theta), -2.0 * index / rotary_dim)
+
+    def dim_of(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+    lo = max(math.floor(dim_of(fast)), 0)
+    hi = min(math.ceil(dim_of(slow)), rotary_dim - 1)
+    ramp = np.clip((index - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    inv_freq = inv_freq / factor * ramp + inv_freq * (1.0 - ramp)
+    magnitude = 0.1 * math.log(factor) + 1.0
+    angles = np.arange(length, dtype=np.float64)[:, None] * inv_freq[None, :]
+    return (np.concatenate([np.cos(angles), np.sin(angles)], axis=1) * magnitude).astype(np.float32)
+
+
 @register_part("position", "rotary")
 class RotaryEncoding(Part):
     """Rotation of pairs over the first `rotary_dim` of each head: `pairing` "half" pairs
@@ -52,6 +77,35 @@ class RotaryEncoding(Part):
         self.table = runtime.shared_table(
             ("rotary", self.theta, self.rotary_dim, length),
             lambda: torch.from_numpy(rotary_table(self.theta, self.rotary_dim, length)))
+
+
+@register_part("position", "yarn_rotary")
+class YarnRotaryEncoding(RotaryEncoding):
+    """`rotary` with YaRN scaling (`yarn_rotary_table`): `factor`, the `original` length, and the
+    numbers of turns `fast` and `slow` between which the frequencies go over from kept to
+    stretched.  The kernels read the table as they read the plain one: the magnitude factor is in
+    its cos and sin."""
+
+    def __init__(self, prefix: str, theta: float, rotary_dim: int, factor: float, original: float,
+                 fast: float, slow: float, max_position: int = 0, pairing: str = "half"):
+        super().__init__(prefix, theta, rotary_dim, max_position, pairing)
+        if factor <= 0 or original <= 0 or fast <= 0 or slow <= 0 or theta <= 1:
+            raise ValueError("yarn_rotary: factor, original, fast and slow must be positive, theta above 1")
+        self.factor, self.original = float(factor), float(original)
+        self.fast, self.slow = float(fast), float(slow)
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        length = max(self.max_position, runtime.max_positions, 1)
+        if self.rotary_dim == 0:
+            self.table = runtime.shared_table(("rotary-none",),
+                                              lambda: torch.zeros((1, 0), dtype=torch.float32))
+            return
+        self.table = runtime.shared_table(
+            ("yarn_rotary", self.theta, self.rotary_dim, length, self.factor, self.original, self.fast,
+             self.slow),
+            lambda: torch.from_numpy(yarn_rotary_table(self.theta, self.rotary_dim, length, self.factor,
+                                                       self.original, self.fast, self.slow)))
 
 
 @register_part("position", "none")

@@ -1,0 +1,113 @@
+"""A feed-forward of routed experts beside an optional expert that every token uses."""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config.spec import PartSpec
+from ..kernels import ops
+from ..weights.tensor_spec import TensorSpec
+from .base import Part, build_part, register_part
+
+
+@register_part("feed_forward", "routed_experts")
+class RoutedExperts(Part):
+    """`experts` gated feed-forwards down(act(gate y) * (up y)) without biases, of which a token
+    uses `top`.
+
+    Router: z = W_r y in 32-bit, s = sigmoid(z) (`scores` "softmax": softmax over the experts).
+    The choice is made on s + correction (a stored vector, `correction`=False: none) and the
+    weights on s without it.  The experts form `groups` equal groups of neighbours; a group's
+    score is the sum of its two largest choice values, and only experts of the `keep` best groups
+    can be chosen.  The `top` largest are taken; their weights are s / (their sum + 1e-20) * `scale`
+    (`normalise`=False: s * scale).  The output is the weighted sum of the chosen experts' outputs,
+    plus - with `shared` (any feed-forward part) - what that part gives for the token.
+
+    All experts' matrices are stacked at bind ([experts, 2 ff, width] gate rows then up rows;
+    [experts, width, ff]).  A step sorts its (token, choice) pairs by expert on the device and runs
+    the two products over tiles of rows that share an expert, so it launches the same kernels
+    whatever the router says.  `names` gives the tensor names below the prefix ("expert" takes the
+    expert's index).
+    """
+
+    NAMES = {"expert": "e{index}.", "gate": "gate", "up": "up", "down": "down", "router": "router",
+             "correction": "correction", "shared": "shared."}
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, experts: int, top: int,
+                 groups: int = 1, keep: int = 1, scale: float = 1.0, scores: str = "sigmoid",
+                 normalise: bool = True, correction: bool = True, activation: str = "silu",
+                 shared: Optional[PartSpec] = None, names: Optional[Dict[str, str]] = None):
+        if activation not in ops.GATE_KINDS:
+            raise ValueError(f"unknown gate activation '{activation}'")
+        if scores not in ("sigmoid", "softmax"):
+            raise ValueError("scores must be 'sigmoid' or 'softmax'")
+        self.prefix, self.hidden_size = prefix, int(hidden_size)
+        self.intermediate_size, self.experts, self.top = int(intermediate_size), int(experts), int(top)
+        self.groups, self.keep, self.scale = int(groups), int(keep), float(scale)
+        self.scores, self.normalise, self.activation = scores, bool(normalise), activation
+        if self.experts <= 0 or not 0 < self.top <= self.experts:
+            raise ValueError("routed_experts: top must lie in 1..experts")
+        if self.groups <= 0 or self.experts % self.groups or not 0 < self.keep <= self.groups:
+            raise ValueError("routed_experts: experts must divide into `groups` groups, keep in 1..groups")
+        if self.top > self.keep * (self.experts // self.groups):
+            raise ValueError("routed_experts: the kept groups hold fewer than `top` experts")
+        self.has_correction = bool(correction)
+        self.names = dict(self.NAMES)
+        self.names.update(names or {})
+        self.shared = None if shared is None else build_part("feed_forward", shared,
+                                                             prefix + self.names["shared"])
+        self.w_router = self.correction = self.w_gate_up = self.w_down = None
+
+    @property
+    def capturable(self) -> bool:
+        return self.shared is None or bool(self.shared.capturable)
+
+    def _expert(self, index: int, which: str) -> str:
+        return self.prefix + self.names["expert"].format(index=index) + self.names[which]
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        h, f = self.hidden_size, self.intermediate_size
+        specs = []
+        for e in range(self.experts):
+            specs += [TensorSpec(self._expert(e, "gate"), (f, h)), TensorSpec(self._expert(e, "up"), (f, h)),
+                      TensorSpec(self._expert(e, "down"), (h, f))]
+        specs.append(TensorSpec(self.prefix + self.names["router"], (self.experts, h)))
+        if self.has_correction:
+            specs.append(TensorSpec(self.prefix + self.names["correction"], (self.experts,), role="vector"))
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
+        self.runtime = runtime
+        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")],
+                                                 tensors[self._expert(e, "up")]])
+                                      for e in range(self.experts)]).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")]
+                                   for e in range(self.experts)]).contiguous()
+        self.w_router = tensors[self.prefix + self.names["router"]].to(torch.float32).contiguous()
+        if self.has_correction:
+            self.correction = tensors[self.prefix + self.names["correction"]].to(torch.float32).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors, runtime)
+
+    def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
+        rt = self.runtime
+        tokens, top = y.shape[0], self.top
+        pairs = tokens * top
+        ids = rt.buffer("routed.ids", tokens, top, torch.int32)
+        weights = rt.buffer("routed.weights", tokens, top, torch.float32)
+        ops.moe_route(y, self.w_router, self.correction, ids, weights, top, self.groups, self.keep,
+                      self.scale, self.scores, self.normalise)
+        lists = ops.moe_align(ids, pairs, self.experts,
+                              rt.buffer("routed.lists", 1, ops.moe_lists_size(pairs, self.experts),
+                                        torch.int32).view(-1))
+        act = rt.buffer("routed.act", pairs, self.intermediate_size, y.dtype)
+        ops.moe_product(y, self.w_gate_up, act, lists, pairs, top, True, self.activation)
+        expert_out = rt.buffer("routed.expert_out", pairs, self.hidden_size, y.dtype)
+        ops.moe_product(act, self.w_down, expert_out, lists, pairs, top, False)
+        shared = None if self.shared is None else self.shared.forward(ctx, y)
+        out = rt.buffer("routed.out", tokens, self.hidden_size, y.dtype)
+        return ops.moe_combine(expert_out, weights, shared, out, top)
