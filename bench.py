@@ -24,7 +24,10 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
 `--workload hybrid` measures the Metulix hybrid design beside the Qwen2 model of equal width, heads,
 feed-forward, depth and window (prefill of one prompt, decode steps of a batch, ms per kind of kernel);
 `--workload zadepel` does the same for the Zadepel design (latent attention, grouped-query attention with
-blended values, minGRU) beside Qwen2 with full causal attention.
+blended values, minGRU) beside Qwen2 with full causal attention; `--workload tapalix` measures the
+Tapalix design (latent attention with and without a rotated part, routed experts beside a shared one,
+a looped stretch of layers) beside a Zadepel model of latent attention layers with a dense feed-forward
+of the width a token uses, at equal depth.
 
 Between timed steps nothing flushes L2: every step streams 15 GB of weights, far more
 than the 126 MB of L2.  `--impl reference` runs the same shape and workload through the
@@ -442,6 +445,40 @@ def zadepel_shapes(width, heads, kv_heads, dim, ff, layers, vocab, window, keep_
     return zadepel, qwen
 
 
+# sizes of the Tapalix comparison: (name, width, heads, head size, rope part, rank, experts, top,
+# groups, kept groups, expert ff, shared ff, layers, passes over the middle layers, vocab)
+TAPALIX_SIZES = (("w2048", 2048, 16, 128, 64, 512, 64, 6, 8, 4, 1408, 2816, 4, 2, 32000),
+                 ("w4096", 4096, 32, 128, 64, 512, 32, 4, 4, 2, 2048, 4096, 3, 2, 32000))
+
+
+def tapalix_shapes(width, heads, dim, rope, rank, experts, top, groups, keep, ff, shared, layers, times, vocab):
+    """A Tapalix model (latent attention with a rotated part and without one in turn, every layer
+    with routed experts beside a shared one, the layers between the first and the last run `times`
+    times) and the closest model the engine had: a Zadepel model of latent attention layers (the
+    same heads, head size, rope part and rank, no window) with a dense gated feed-forward as wide as
+    what a Tapalix token uses (top x expert ff + shared ff), one layer per layer run."""
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "shared": {"ff": shared},
+           "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": groups, "keep": keep}}}
+    rotated = {"type": "latent_attention", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": rope, "vdim": dim, "kv_rank": rank, "scale": (dim + rope) ** -0.5,
+        "rot": {"base": 10000.0, "dims": rope,
+                "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}}
+    gated = {"type": "latent_attention_2", "mlp": mlp, "mixer": {
+        "heads": heads, "dim": dim, "vdim": dim, "kv_rank": rank, "scale": dim ** -0.5}}
+    stop = max(layers - 1, 2)
+    tapalix = {"architecture": "Tapalix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "embedding": {"scale": 1.0}, "logit_scale": 1.0, "logit_softcap": 30.0,
+               "loop": {"start": 1, "stop": stop, "times": times},
+               "layers": [rotated if i % 2 == 0 else gated for i in range(layers)]}
+    runs = layers + (times - 1) * (stop - 1)
+    latent = {"type": "latent_attention", "mlp": {"kind": "dense", "ff": top * ff + shared}, "mixer": {
+        "heads": heads, "dim": dim, "rot_dim": rope, "vdim": dim, "kv_rank": rank, "scale": (dim + rope) ** -0.5,
+        "rot": {"base": 10000.0, "dims": rope}}}
+    zadepel = {"architecture": "Zadepel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "layers": [latent] * runs}
+    return tapalix, zadepel
+
+
 def hybrid_workload(args, design="metulix") -> int:
     """The Metulix design (or, `design`, the Zadepel design) beside the Qwen2 model of equal size
     (random bf16 weights): prefill of
@@ -476,7 +513,9 @@ def hybrid_workload(args, design="metulix") -> int:
                                "layernorm_rows", "add_layernorm", "cast_rows", "silu_rows", "lightning_scan",
                                "gated_rmsnorm", "conv_norm_rotate", "conv_tails", "talking_attention",
                                "talking_attention_mma", "norm_add_norm", "gated_act", "mingru_scan",
-                               "scaled_attention", "rotate_mix_write", "latent_prep", "head_product")
+                               "scaled_attention", "rotate_mix_write", "latent_prep", "head_product",
+                               "sum_layernorm", "settle_concat", "logit_cap", "sigmoid_gate", "moe_route",
+                               "moe_align", "moe_product", "moe_combine")
              if hasattr(ops, name)]
 
     def by_kind(fn):
@@ -512,17 +551,31 @@ def hybrid_workload(args, design="metulix") -> int:
         out["(whole step)"] = total
         return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
 
-    sizes = [s for s in HYBRID_SIZES if not args.sizes or s[0] in args.sizes.split(",")]
+    table = TAPALIX_SIZES if design == "tapalix" else HYBRID_SIZES
+    sizes = [s for s in table if not args.sizes or s[0] in args.sizes.split(",")]
     results = []
     clocks = ClockSampler()
     clocks.start()
-    for name, width, heads, kv_heads, dim, ff, layers, vocab in sizes:
-        layers = args.layers or layers
-        shapes = (zadepel_shapes if design == "zadepel" else hybrid_shapes)(
-            width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first)
-        entry = {"size": name, "width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
-                 "ff": ff, "layers": layers, "vocab": vocab, "window": window, "keep_first": keep_first}
-        for name_of_design, shape in zip((design, "qwen2"), shapes):
+    for size in sizes:
+        if design == "tapalix":
+            name, width, heads, dim, rope, rank, experts, top, groups, keep, ff, shared, layers, times, vocab = size
+            layers = args.layers or layers
+            shapes = tapalix_shapes(width, heads, dim, rope, rank, experts, top, groups, keep, ff, shared,
+                                    layers, times, vocab)
+            entry = {"size": name, "width": width, "heads": heads, "head_dim": dim, "rope_dim": rope,
+                     "kv_rank": rank, "experts": experts, "top": top, "groups": [groups, keep],
+                     "expert_ff": ff, "shared_ff": shared, "layers": layers, "passes": times,
+                     "layer_runs": len(shapes[1]["layers"]), "vocab": vocab}
+            beside = "zadepel"
+        else:
+            name, width, heads, kv_heads, dim, ff, layers, vocab = size
+            layers = args.layers or layers
+            shapes = (zadepel_shapes if design == "zadepel" else hybrid_shapes)(
+                width, heads, kv_heads, dim, ff, layers, vocab, window, keep_first)
+            entry = {"size": name, "width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
+                     "ff": ff, "layers": layers, "vocab": vocab, "window": window, "keep_first": keep_first}
+            beside = "qwen2"
+        for name_of_design, shape in zip((design, beside), shapes):
             config = config_from_dict(shape)
             model = LoadedModel.from_random(config, seed=0, std=0.02, dtype=compute,
                                             max_positions=max(context, prompt_len) + 64)
@@ -588,7 +641,8 @@ def hybrid_workload(args, design="metulix") -> int:
         results.append(entry)
     clock_record = clocks.stop()
     print(json.dumps({
-        "metric": f"prefill and decode tokens/s of the {design.capitalize()} design beside Qwen2 at equal size",
+        "metric": f"prefill and decode tokens/s of the {design.capitalize()} design beside "
+                  f"{'Zadepel' if design == 'tapalix' else 'Qwen2'} at equal size",
         "impl": "engine", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "dtype": "bf16" if compute == "bfloat16" else "fp32",
         "config": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context,
@@ -678,13 +732,14 @@ def main() -> int:
                              "blocks it falls to instead of sharing it out among all (for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid", "zadepel"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid", "zadepel", "tapalix"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
                              "8,192-token contexts and chunked prefill of an 8,192-token prompt; "
                              "timeline: kernel start and end times inside one decode step (text); "
                              "hybrid: the Metulix design beside Qwen2 at equal sizes, prefill and decode; "
-                             "zadepel: the same for the Zadepel design")
+                             "zadepel: the same for the Zadepel design; "
+                             "tapalix: the Tapalix design beside a Zadepel model of latent attention layers")
     parser.add_argument("--sizes", default="", help="hybrid: which sizes to run (w2048,w4096; '' = all)")
     parser.add_argument("--requests", type=int, default=256)
     parser.add_argument("--step-tokens", type=int, default=2048, help="serving: token budget of one step")
@@ -710,6 +765,8 @@ def main() -> int:
         return hybrid_workload(args)
     if args.workload == "zadepel":
         return hybrid_workload(args, design="zadepel")
+    if args.workload == "tapalix":
+        return hybrid_workload(args, design="tapalix")
 
     import numpy as np
     import torch

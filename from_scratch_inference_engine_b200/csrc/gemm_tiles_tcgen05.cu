@@ -85,6 +85,12 @@ struct TileGemmParams {
     float* workspace;               // [shared tile][part][block of the pair][128 rows][256 columns]
     int* counters;                  // [shared tile][block of the pair][quarter], zero between launches
     int* error;
+    // grouped form: w is [groups x group_rows, K]; the rows of x were sorted by group and every
+    // group's rows start on a tile boundary; tile_group[m] is the group of row tile m, and only
+    // the first *tiles_used row tiles hold rows (both written by a kernel earlier in the stream)
+    const int* tile_group;
+    const int* tiles_used;
+    int group_rows;
 };
 
 // One piece of work of a pair: k-blocks [kb0, kb1) of a tile.  shared >= 0: the tile is the
@@ -261,7 +267,7 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     const int rank = (int)cluster_rank();            // 0: the block that issues the MMAs
     const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
     const int kblocks = (p.K + BK - 1) / BK;
-    const int total_tiles = p.m_tiles * p.n_tiles;
+    int m_tiles = p.m_tiles, total_tiles = p.m_tiles * p.n_tiles;     // the grouped form learns them below
     // Order of the tiles: bands of up to RASTER_M tiles of rows, inside a band the rows run
     // fastest.  The pairs of blocks work on consecutive tiles at the same time, so a wave of
     // them covers a roughly square patch of y and fetches as few rows of x and w as 74 tiles
@@ -271,12 +277,12 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     constexpr int RASTER_M = 8;
     auto tile_m = [&](int tile) {
         const int band = tile / (RASTER_M * p.n_tiles), first = band * RASTER_M;
-        const int height = min(RASTER_M, p.m_tiles - first);
+        const int height = min(RASTER_M, m_tiles - first);
         return first + (tile - band * RASTER_M * p.n_tiles) % height;
     };
     auto tile_n = [&](int tile) {
         const int band = tile / (RASTER_M * p.n_tiles), first = band * RASTER_M;
-        const int height = min(RASTER_M, p.m_tiles - first);
+        const int height = min(RASTER_M, m_tiles - first);
         return (tile - band * RASTER_M * p.n_tiles) / height;
     };
     constexpr int TILE_COLS = EPI == EPI_SWIGLU ? TILE / 2 : TILE;      // output columns per tile
@@ -300,13 +306,17 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
     // x is the output of the kernel before this one; the kernel after this one may set up now
     grid_dependency_wait();
     grid_dependents_go();
+    if (p.tiles_used) {     // every thread of every pair reads the same number: all roles walk the same tiles
+        m_tiles = min(m_tiles, *p.tiles_used);
+        total_tiles = m_tiles * p.n_tiles;
+    }
 
     if (warp == 0 && lane == 0) {
         // ------------------------------------------------------------ TMA producer (both blocks)
         int it = 0, issued = 0;
         bool ok = true;
         auto w_row_of = [&](int tile) {
-            const int n0 = tile_n(tile) * TILE_COLS;
+            const int n0 = tile_n(tile) * TILE_COLS + (p.tile_group ? p.tile_group[tile_m(tile)] * p.group_rows : 0);
             return EPI == EPI_SWIGLU ? (rank == 0 ? n0 : p.up_row0 + n0) : n0 + rank * HALF;
         };
         WorkItem work;
@@ -737,10 +747,48 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
     if (p.share_pairs > 0 && (!workspace || !counters || workspace_floats < need_floats || counters_len < need_counters))
         p.share_pairs = 0;
     p.workspace = workspace; p.counters = counters;
+    p.tile_group = nullptr; p.tiles_used = nullptr; p.group_rows = 0;
     p.y = y; p.ldy = ldy; p.bias = (const bf16*)bias;
     p.up_row0 = N; p.out_f32 = out_f32; p.error = error; p.gate = swiglu;
     // the copy engine writes y when its rows start on 16-byte boundaries; else the lanes store their rows
     p.tma_store = !out_f32 && ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
+    CUtensorMap map_y = map_x;
+    if (p.tma_store) {
+        rc = make_out_map(&map_y, y, M, N, ldy);
+        if (rc != 0) return rc;
+    }
+    return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
+}
+
+// The grouped form: the rows of x [M, K] were sorted by group, every group's rows start on a
+// multiple of 256 (M is the room there is, a multiple of 256; rows that no group owns hold anything),
+// w is [groups x group_rows, K] with a group's matrix in group_rows consecutive rows ([gate rows (N);
+// up rows (N)] for swiglu).  tile_group[m] names the group of row tile m and tiles_used[0] how many row
+// tiles hold rows; both live on the device and are read after the kernel before this one has finished.
+// y[M, N] gets every used row tile's rows (columns of a tile beyond N meet the next group's rows and
+// are never stored).
+int fsie_gemm_tiles_grouped(const void* weight_map, const void* x, long long ldx, void* y, long long ldy,
+                            int M, int N, int K, int swiglu, int blocks, const int* tile_group,
+                            const int* tiles_used, int group_rows, int* error, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || swiglu < 0 ||
+        swiglu > 2 || M % TILE != 0 || !tile_group || !tiles_used || group_rows <= 0)
+        return ERR_BAD_ARGUMENT;
+    CUtensorMap map_w, map_x;
+    memcpy(&map_w, weight_map, sizeof(map_w));
+    int rc = make_map(&map_x, x, M, K, ldx);
+    if (rc != 0) return rc;
+    TileGemmParams p;
+    int pairs = 0, need_counters = 0;
+    long long need_floats = 0;
+    rc = plan(M, N, K, swiglu, blocks, p, &pairs, &need_floats, &need_counters);
+    if (rc != 0) return rc;
+    p.share_pairs = 0;          // how many tiles there are is known on the device only: no tile is shared
+    p.workspace = nullptr; p.counters = nullptr;
+    p.tile_group = tile_group; p.tiles_used = tiles_used; p.group_rows = group_rows;
+    p.y = y; p.ldy = ldy; p.bias = nullptr;
+    p.up_row0 = N; p.out_f32 = 0; p.error = error; p.gate = swiglu;
+    p.tma_store = ldy % 8 == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0;
     CUtensorMap map_y = map_x;
     if (p.tma_store) {
         rc = make_out_map(&map_y, y, M, N, ldy);

@@ -40,8 +40,11 @@ __device__ __forceinline__ int warp_argmax(const float* v, const unsigned char* 
     return at;
 }
 
+// y == nullptr: the router's logits were computed by a matrix product and wait in `logits`
+// [tokens, experts]; the block (one warp then) only scores, chooses and weighs.
 template <typename T>
 __global__ void moe_route_kernel(const T* __restrict__ y, int y_ld, const float* __restrict__ w_router,
+                                 const float* __restrict__ logits,
                                  const float* __restrict__ correction, int* __restrict__ ids,
                                  float* __restrict__ weights, int width, int experts, int top, int groups,
                                  int keep, float scale, int softmax_scores, int normalise) {
@@ -55,15 +58,19 @@ __global__ void moe_route_kernel(const T* __restrict__ y, int y_ld, const float*
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
     grid_dependency_wait();
     grid_dependents_go();
-    const T* yr = y + (size_t)t * y_ld;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_float(yr[c]);
-    __syncthreads();
-    for (int e = warp; e < experts; e += warps) {
-        const float* wr = w_router + (size_t)e * width;
-        float acc = 0.f;
-        for (int c = lane; c < width; c += 32) acc = fmaf(wr[c], row[c], acc);
-        acc = warp_sum(acc);
-        if (lane == 0) score[e] = acc;
+    if (y) {
+        const T* yr = y + (size_t)t * y_ld;
+        for (int c = threadIdx.x; c < width; c += blockDim.x) row[c] = to_float(yr[c]);
+        __syncthreads();
+        for (int e = warp; e < experts; e += warps) {
+            const float* wr = w_router + (size_t)e * width;
+            float acc = 0.f;
+            for (int c = lane; c < width; c += 32) acc = fmaf(wr[c], row[c], acc);
+            acc = warp_sum(acc);
+            if (lane == 0) score[e] = acc;
+        }
+    } else {
+        for (int e = threadIdx.x; e < experts; e += blockDim.x) score[e] = logits[(size_t)t * experts + e];
     }
     __syncthreads();
     if (warp != 0) return;
@@ -124,11 +131,13 @@ __global__ void moe_route_kernel(const T* __restrict__ y, int y_ld, const float*
 }
 
 // ------------------------------------------------------------------- pairs sorted by expert
-// One block.  offsets[e] .. offsets[e + 1]: the rows of expert e in `sorted` (pair = token * top +
-// choice).  tiles: (expert, first row) of every tile of MOE_TILE rows; meta[0] = their number.
-__global__ void moe_align_kernel(const int* __restrict__ ids, int pairs, int experts, int* __restrict__ offsets,
-                                 int* __restrict__ sorted, int* __restrict__ tile_expert,
-                                 int* __restrict__ tile_row0, int* __restrict__ meta) {
+// One block.  Compact layout: offsets[e] .. offsets[e + 1] are the rows of expert e in `sorted`
+// (pair = token * top + choice); tiles: (expert, first row) of every tile of `tile` rows; meta[0] =
+// their number.  Padded layout (`padded`): every expert's rows start on a multiple of `tile`, rows
+// that no pair owns hold -1, offsets[e] is the expert's first row, and place[pair] is the pair's row.
+__global__ void moe_align_kernel(const int* __restrict__ ids, int pairs, int experts, int tile, int padded,
+                                 int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ tile_expert,
+                                 int* __restrict__ tile_row0, int* __restrict__ meta, int* __restrict__ place) {
     extern __shared__ int align_smem[];
     int* count = align_smem;                    // [experts]
     int* start = count + experts;               // [experts + 1]
@@ -145,12 +154,12 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int pairs, int exp
     if (threadIdx.x == 0) {
         int rows = 0, tiles = 0;
         for (int e = 0; e < experts; ++e) {
-            start[e] = rows;
+            start[e] = padded ? tiles * tile : rows;
             tile_start[e] = tiles;
             rows += count[e];
-            tiles += (count[e] + MOE_TILE - 1) / MOE_TILE;
+            tiles += (count[e] + tile - 1) / tile;
         }
-        start[experts] = rows;
+        start[experts] = padded ? tiles * tile : rows;
         tile_start[experts] = tiles;
         meta[0] = tiles;
     }
@@ -160,17 +169,40 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int pairs, int exp
         const int n = tile_start[e + 1] - tile_start[e];
         for (int i = 0; i < n; ++i) {
             tile_expert[tile_start[e] + i] = e;
-            tile_row0[tile_start[e] + i] = start[e] + i * MOE_TILE;
+            tile_row0[tile_start[e] + i] = start[e] + i * tile;
         }
         count[e] = 0;                           // from here on: how many rows of e are placed
     }
+    if (padded)
+        for (int r = threadIdx.x; r < start[experts]; r += blockDim.x) sorted[r] = -1;
     __syncthreads();
     // a pair's place among its expert's rows: in the order the threads arrive.  Each row of a
     // product is summed on its own, so the order of an expert's rows changes no result.
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = ids[p];
-        if (e >= 0 && e < experts) sorted[start[e] + atomicAdd(&count[e], 1)] = p;
+        if (e < 0 || e >= experts) continue;
+        const int at = start[e] + atomicAdd(&count[e], 1);
+        sorted[at] = p;
+        if (place) place[p] = at;
     }
+}
+
+// x_sorted[r] = x[sorted[r] / top] for the rows of the used tiles (zeros where no pair owns the row):
+// the rows of the step's tokens in the padded order, for a product that reads whole tiles.
+__global__ void moe_gather_kernel(const bf16* __restrict__ x, long long x_ld, const int* __restrict__ sorted,
+                                  const int* __restrict__ meta, int tile, int top, bf16* __restrict__ out, int k) {
+    grid_dependency_wait();
+    grid_dependents_go();
+    const int r = blockIdx.x;
+    if (r >= meta[0] * tile) return;
+    const int pair = sorted[r];
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)r * k);
+    if (pair < 0) {
+        for (int c = threadIdx.x; c < k / 8; c += blockDim.x) dst[c] = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(pair / top) * x_ld);
+    for (int c = threadIdx.x; c < k / 8; c += blockDim.x) dst[c] = src[c];
 }
 
 // --------------------------------------------------------------- tiled products, any type
@@ -392,14 +424,17 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(
 // -------------------------------------------------------------------------------- combine
 template <typename T>
 __global__ void moe_combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weights,
-                                   const T* __restrict__ shared, T* __restrict__ out, int width, int top) {
+                                   const T* __restrict__ shared, const int* __restrict__ place,
+                                   T* __restrict__ out, int width, int top) {
     grid_dependency_wait();
     grid_dependents_go();
     const size_t t = blockIdx.x;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float acc = 0.f;
-        for (int j = 0; j < top; ++j)
-            acc = fmaf(weights[t * top + j], to_float(expert_out[(t * top + j) * width + c]), acc);
+        for (int j = 0; j < top; ++j) {
+            const size_t row = place ? (size_t)place[t * top + j] : t * top + j;
+            acc = fmaf(weights[t * top + j], to_float(expert_out[row * width + c]), acc);
+        }
         if (shared) acc += to_float(shared[t * width + c]);
         out[t * width + c] = from_float<T>(acc);
     }
@@ -415,39 +450,53 @@ int fsie_moe_tile_rows() { return MOE_TILE; }
 
 // y [tokens, y_ld] of the storage type; w_router float32 [experts, width]; correction float32
 // [experts] or null; ids int32 / weights float32 [tokens, top].
-int fsie_moe_route(const void* y, int y_ld, const float* w_router, const float* correction, int* ids,
+int fsie_moe_route(const void* y, int y_ld, const float* w_router, const float* logits, const float* correction, int* ids,
                    float* weights, int tokens, int width, int experts, int top, int groups, int keep,
                    float scale, int softmax_scores, int normalise, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (width <= 0 || experts <= 0 || top <= 0 || top > experts || groups <= 0 || experts % groups ||
+    if ((y && width <= 0) || experts <= 0 || top <= 0 || top > experts || groups <= 0 || experts % groups ||
         keep <= 0 || keep > groups || top > keep * (experts / groups))
         return ERR_BAD_ARGUMENT;
+    if (!y && !logits) return ERR_BAD_ARGUMENT;
+    if (!y) width = 0;
+    const int threads = y ? 128 : 32;
     const size_t smem = ((size_t)width + 2 * experts + groups) * sizeof(float) + experts + groups + 8;
     if (smem > 200 * 1024) return ERR_UNSUPPORTED;
     if (dtype == DTYPE_F32) {
         if (smem > 48 * 1024)
             cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return launch_dependent(moe_route_kernel<float>, tokens, 128, smem, stream, (const float*)y, y_ld, w_router,
-                                correction, ids, weights, width, experts, top, groups, keep, scale,
+        return launch_dependent(moe_route_kernel<float>, tokens, threads, smem, stream, (const float*)y, y_ld, w_router,
+                                logits, correction, ids, weights, width, experts, top, groups, keep, scale,
                                 softmax_scores, normalise);
     }
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_dependent(moe_route_kernel<bf16>, tokens, 128, smem, stream, (const bf16*)y, y_ld, w_router,
-                            correction, ids, weights, width, experts, top, groups, keep, scale, softmax_scores,
+    return launch_dependent(moe_route_kernel<bf16>, tokens, threads, smem, stream, (const bf16*)y, y_ld, w_router,
+                            logits, correction, ids, weights, width, experts, top, groups, keep, scale, softmax_scores,
                             normalise);
 }
 
-// offsets [experts + 1], sorted [pairs], tile_expert / tile_row0 [pairs / tile + experts], meta [1]
-int fsie_moe_align(const int* ids, int pairs, int experts, int* offsets, int* sorted, int* tile_expert,
-                   int* tile_row0, int* meta, cudaStream_t stream) {
+// offsets [experts + 1], sorted [pairs] (padded: [(pairs / tile + experts) * tile]), tile_expert /
+// tile_row0 [pairs / tile + experts], meta [1], place [pairs] or null
+int fsie_moe_align(const int* ids, int pairs, int experts, int tile, int padded, int* offsets, int* sorted,
+                   int* tile_expert, int* tile_row0, int* meta, int* place, cudaStream_t stream) {
     if (pairs <= 0) return 0;
-    if (experts <= 0) return ERR_BAD_ARGUMENT;
+    if (experts <= 0 || tile <= 0 || (!padded && tile != MOE_TILE)) return ERR_BAD_ARGUMENT;
     const size_t smem = (3 * (size_t)experts + 2) * sizeof(int);
     if (smem > 40 * 1024) return ERR_UNSUPPORTED;
     const int threads = pairs >= 4096 ? 1024 : (pairs >= 512 ? 256 : 64);
-    return launch_dependent(moe_align_kernel, 1, threads, smem, stream, ids, pairs, experts, offsets, sorted,
-                            tile_expert, tile_row0, meta);
+    return launch_dependent(moe_align_kernel, 1, threads, smem, stream, ids, pairs, experts, tile, padded, offsets,
+                            sorted, tile_expert, tile_row0, meta, place);
+}
+
+// out [rows of the padded layout, k] bf16 = the tokens' rows of x in that order; `rows` is the room
+// there is (pairs / tile + experts tiles).
+int fsie_moe_gather(const void* x, long long x_ld, const int* sorted, const int* meta, int tile, int top,
+                    void* out, int rows, int k, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (k <= 0 || k % 8 || x_ld % 8 || ((((size_t)x) | ((size_t)out)) & 15)) return ERR_BAD_ARGUMENT;
+    return launch_dependent(moe_gather_kernel, rows, k >= 2048 ? 256 : 128, 0, stream, (const bf16*)x, x_ld, sorted,
+                            meta, tile, top, (bf16*)out, k);
 }
 
 // gated = 1: x [tokens, x_ld] read at pair / top, w [experts, 2 n, k] (gate rows, then up rows), out
@@ -479,17 +528,17 @@ int fsie_moe_product(const void* x, long long x_ld, const void* w, void* out, lo
 #undef FSIE_MOE
 }
 
-// expert_out [tokens * top, width] at the pairs' rows; weights float32 [tokens, top]; shared
-// [tokens, width] or null; out [tokens, width].
-int fsie_moe_combine(const void* expert_out, const float* weights, const void* shared, void* out, int tokens,
-                     int width, int top, int dtype, cudaStream_t stream) {
+// expert_out [tokens * top, width] at the pairs' rows (or, with `place`, pair p at row place[p]);
+// weights float32 [tokens, top]; shared [tokens, width] or null; out [tokens, width].
+int fsie_moe_combine(const void* expert_out, const float* weights, const void* shared, const int* place, void* out,
+                     int tokens, int width, int top, int dtype, cudaStream_t stream) {
     if (tokens <= 0 || width <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == DTYPE_F32)
         return launch_dependent(moe_combine_kernel<float>, tokens, threads, 0, stream, (const float*)expert_out,
-                                weights, (const float*)shared, (float*)out, width, top);
+                                weights, (const float*)shared, place, (float*)out, width, top);
     return launch_dependent(moe_combine_kernel<bf16>, tokens, threads, 0, stream, (const bf16*)expert_out, weights,
-                            (const bf16*)shared, (bf16*)out, width, top);
+                            (const bf16*)shared, place, (bf16*)out, width, top);
 }
 
 }  // extern "C"

@@ -651,8 +651,9 @@ def gemm_tiles_lib():
         lib.fsie_gemm_tiles.argtypes = [p, p, ll, p, ll, p, i, i, i, i, i, i, p, ll, p, i, p, p]
         lib.fsie_gemm_tiles_workspace.argtypes = [i, i, i, i, i, ctypes.POINTER(ll), ctypes.POINTER(i)]
         lib.fsie_gemm_tiles_pairs.argtypes = []
+        lib.fsie_gemm_tiles_grouped.argtypes = [p, p, ll, p, ll, i, i, i, i, i, p, p, i, p, p]
         for name in ("fsie_gemm_tiles_map_bytes", "fsie_gemm_tiles_weight_map", "fsie_gemm_tiles",
-                     "fsie_gemm_tiles_pairs", "fsie_gemm_tiles_workspace"):
+                     "fsie_gemm_tiles_pairs", "fsie_gemm_tiles_workspace", "fsie_gemm_tiles_grouped"):
             getattr(lib, name).restype = i
         pairs = lib.fsie_gemm_tiles_pairs()       # also sets the kernels up, outside any capture
         if pairs <= 0:
@@ -731,6 +732,53 @@ def gemm_tiles(weight: TiledWeight, x: torch.Tensor, out: torch.Tensor,
         _ptr(workspace), workspace.numel() if workspace is not None else 0,
         _ptr(counters), counters.numel() if counters is not None else 0, _ptr(error),
         _stream()), "gemm_tiles")
+    return out
+
+
+GEMM_TILES_ROWS = 256     # rows of a tile of `gemm_tiles`: a group's rows start on a multiple of it
+
+
+class GroupedTiledWeight:
+    """Bfloat16 matrices [groups, rows, K] of equal shape prepared for `gemm_tiles_grouped`: one TMA
+    descriptor over all of them.  For SwiGLU each matrix holds the gate rows and then as many up
+    rows."""
+
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False, activation: str = "silu"):
+        _need(weight, torch.bfloat16, "weight")
+        self.gate = 1 + GATE_KINDS[activation] if swiglu else 0
+        groups, rows, k = weight.shape
+        if k % 8 or (swiglu and rows % 2):
+            raise KernelError("gemm_tiles_grouped: K must be a multiple of 8, a SwiGLU matrix hold "
+                              "gate rows and as many up rows")
+        lib = gemm_tiles_lib()
+        self.weight, self.swiglu, self.k, self.groups, self.rows = weight, swiglu, k, groups, rows
+        self.n = rows // 2 if swiglu else rows
+        self.map = ctypes.create_string_buffer(lib.fsie_gemm_tiles_map_bytes() + 64)
+        offset = (-ctypes.addressof(self.map)) % 64
+        self.map_ptr = ctypes.c_void_p(ctypes.addressof(self.map) + offset)
+        _check(lib.fsie_gemm_tiles_weight_map(self.map_ptr, _ptr(weight), groups * rows, k),
+               "gemm_tiles_grouped weight map")
+
+
+def gemm_tiles_grouped(weight: GroupedTiledWeight, x: torch.Tensor, out: torch.Tensor,
+                       tile_group: torch.Tensor, tiles_used: torch.Tensor, error: torch.Tensor,
+                       blocks: int) -> torch.Tensor:
+    """Row tile m of x (256 rows, all of one group) times the matrix of group tile_group[m]:
+    out[r] = x[r] @ w[g].T, or silu(x[r] @ gate[g].T) * (x[r] @ up[g].T).  x [M, K] and out [M, N]
+    are bfloat16 with M a multiple of 256; only the first tiles_used[0] row tiles are computed (both
+    lists are int32 on the device, written by a kernel earlier in the stream)."""
+    _need(x, torch.bfloat16, "x")
+    _need(out, torch.bfloat16, "out")
+    _need(tile_group, torch.int32, "tile_group")
+    _need(tiles_used, torch.int32, "tiles_used")
+    rows, k = x.shape
+    if k != weight.k or rows % GEMM_TILES_ROWS or out.shape[0] != rows or out.shape[1] != weight.n or \
+            tile_group.numel() < rows // GEMM_TILES_ROWS:
+        raise KernelError("gemm_tiles_grouped: shapes do not fit")
+    _check(gemm_tiles_lib().fsie_gemm_tiles_grouped(
+        weight.map_ptr, _ptr(x), x.stride(0), _ptr(out), out.stride(0), rows, weight.n, k, weight.gate,
+        blocks, _ptr(tile_group), _ptr(tiles_used), weight.rows, _ptr(error), _stream()),
+        "gemm_tiles_grouped")
     return out
 
 
@@ -1348,12 +1396,13 @@ def routed():
         lib.fsie_logit_cap.argtypes = [p, ll, f, f, p]
         lib.fsie_sigmoid_gate.argtypes = [p, i, p, i, i, i, i, p]
         lib.fsie_moe_tile_rows.argtypes = []
-        lib.fsie_moe_route.argtypes = [p, i, p, p, p, p, i, i, i, i, i, i, f, i, i, i, p]
-        lib.fsie_moe_align.argtypes = [p, i, i, p, p, p, p, p, p]
+        lib.fsie_moe_route.argtypes = [p, i, p, p, p, p, p, i, i, i, i, i, i, f, i, i, i, p]
+        lib.fsie_moe_align.argtypes = [p, i, i, i, i, p, p, p, p, p, p, p]
+        lib.fsie_moe_gather.argtypes = [p, ll, p, p, i, i, p, i, i, p]
         lib.fsie_moe_product.argtypes = [p, ll, p, p, ll, p, p, p, p, p, i, i, i, i, i, i, i, i, p]
-        lib.fsie_moe_combine.argtypes = [p, p, p, p, i, i, i, i, p]
+        lib.fsie_moe_combine.argtypes = [p, p, p, p, p, i, i, i, i, p]
         for name in ("fsie_sum_layernorm", "fsie_settle_concat", "fsie_logit_cap", "fsie_sigmoid_gate",
-                     "fsie_moe_tile_rows", "fsie_moe_route", "fsie_moe_align", "fsie_moe_product",
+                     "fsie_moe_tile_rows", "fsie_moe_route", "fsie_moe_align", "fsie_moe_gather", "fsie_moe_product",
                      "fsie_moe_combine"):
             getattr(lib, name).restype = i
         _routed = lib
@@ -1447,51 +1496,85 @@ def moe_tile_rows() -> int:
     return routed().fsie_moe_tile_rows()
 
 
-def moe_route(y: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor],
+def moe_route(y: Optional[torch.Tensor], w_router: Optional[torch.Tensor], correction: Optional[torch.Tensor],
               ids: torch.Tensor, weights: torch.Tensor, top: int, groups: int, keep: int, scale: float,
-              scores: str = "sigmoid", normalise: bool = True) -> None:
-    """Per token: s = sigmoid (or softmax) of w_router y in 32-bit; the `top` experts with the largest
-    s + correction among the `keep` best of `groups` groups (a group's score: its two largest);
-    weights s / (their sum + 1e-20) * scale.  ids int32, weights float32, both [tokens, top]."""
-    _need(y, None, "y", contiguous=False)
-    _need(w_router, torch.float32, "w_router")
+              scores: str = "sigmoid", normalise: bool = True, logits: Optional[torch.Tensor] = None) -> None:
+    """Per token: s = sigmoid (or softmax) of the router's logits in 32-bit; the `top` experts with the
+    largest s + correction among the `keep` best of `groups` groups (a group's score: its two
+    largest); weights s / (their sum + 1e-20) * scale.  The logits are w_router y, summed here
+    (w_router float32 [experts, width]) or - `logits`, float32 [tokens, experts] - by a product
+    before this call.  ids int32, weights float32, both [tokens, top]."""
     _need(ids, torch.int32, "ids")
     _need(weights, torch.float32, "weights")
-    tokens, width = y.shape
-    experts = w_router.shape[0]
     if correction is not None:
         _need(correction, torch.float32, "correction")
-    if w_router.shape[1] != width or ids.numel() < tokens * top or weights.numel() < tokens * top or \
-            y.stride(1) != 1 or scores not in ("sigmoid", "softmax"):
+    if scores not in ("sigmoid", "softmax"):
+        raise KernelError("moe_route: scores must be 'sigmoid' or 'softmax'")
+    if logits is not None:
+        _need(logits, torch.float32, "logits")
+        tokens, experts = logits.shape
+        y_ptr, y_ld, width, tag, w_ptr = None, 0, 0, DTYPE_F32, None
+    else:
+        _need(y, None, "y", contiguous=False)
+        _need(w_router, torch.float32, "w_router")
+        tokens, width = y.shape
+        experts = w_router.shape[0]
+        if w_router.shape[1] != width or y.stride(1) != 1:
+            raise KernelError("moe_route: shapes do not fit")
+        y_ptr, y_ld, tag, w_ptr = _ptr(y), y.stride(0), _tag(y.dtype), _ptr(w_router)
+    if ids.numel() < tokens * top or weights.numel() < tokens * top or \
+            (correction is not None and correction.numel() != experts):
         raise KernelError("moe_route: shapes do not fit")
-    _check(routed().fsie_moe_route(_ptr(y), y.stride(0), _ptr(w_router), _ptr(correction), _ptr(ids),
+    _check(routed().fsie_moe_route(y_ptr, y_ld, w_ptr, _ptr(logits), _ptr(correction), _ptr(ids),
                                    _ptr(weights), tokens, width, experts, int(top), int(groups), int(keep),
-                                   float(scale), int(scores == "softmax"), int(normalise), _tag(y.dtype),
+                                   float(scale), int(scores == "softmax"), int(normalise), tag,
                                    _stream()), "moe_route")
 
 
-def moe_align(ids: torch.Tensor, pairs: int, experts: int, lists: torch.Tensor) -> Tuple[torch.Tensor, ...]:
+def moe_align(ids: torch.Tensor, pairs: int, experts: int, lists: torch.Tensor,
+              tile: int = 0, padded: bool = False) -> Tuple[torch.Tensor, ...]:
     """Sort the (token, choice) pairs by expert.  `lists` is int32 working memory of at least
-    `moe_lists_size(pairs, experts)` entries; returns its views (offsets [experts + 1], sorted [pairs],
-    tile_expert, tile_row0, meta [1])."""
+    `moe_lists_size(pairs, experts, tile, padded)` entries; returns its views (offsets [experts + 1],
+    sorted, tile_expert, tile_row0, meta [1], place).  Compact layout: sorted [pairs] holds the pairs
+    expert after expert, place is None.  `padded`: every expert's rows start on a multiple of `tile`,
+    sorted [(pairs // tile + experts) * tile] holds -1 where no pair owns the row, place [pairs] is
+    each pair's row."""
     _need(ids, torch.int32, "ids")
     _need(lists, torch.int32, "lists")
-    tiles = pairs // moe_tile_rows() + experts
-    if lists.numel() < moe_lists_size(pairs, experts) or ids.numel() < pairs:
+    tile = tile or moe_tile_rows()
+    tiles = pairs // tile + experts
+    if lists.numel() < moe_lists_size(pairs, experts, tile, padded) or ids.numel() < pairs:
         raise KernelError("moe_align: working memory is too small")
     cut = 0
     views = []
-    for n in (experts + 1, pairs, tiles, tiles, 1):
+    for n in (experts + 1, tiles * tile if padded else pairs, tiles, tiles, 1, pairs if padded else 0):
         views.append(lists[cut:cut + n])
         cut += n
-    offsets, order, tile_expert, tile_row0, meta = views
-    _check(routed().fsie_moe_align(_ptr(ids), pairs, experts, _ptr(offsets), _ptr(order), _ptr(tile_expert),
-                                   _ptr(tile_row0), _ptr(meta), _stream()), "moe_align")
-    return offsets, order, tile_expert, tile_row0, meta
+    offsets, order, tile_expert, tile_row0, meta, place = views
+    _check(routed().fsie_moe_align(_ptr(ids), pairs, experts, tile, int(padded), _ptr(offsets), _ptr(order),
+                                   _ptr(tile_expert), _ptr(tile_row0), _ptr(meta),
+                                   _ptr(place) if padded else None, _stream()), "moe_align")
+    return offsets, order, tile_expert, tile_row0, meta, (place if padded else None)
 
 
-def moe_lists_size(pairs: int, experts: int) -> int:
-    return experts + 1 + pairs + 2 * (pairs // moe_tile_rows() + experts) + 1
+def moe_lists_size(pairs: int, experts: int, tile: int = 0, padded: bool = False) -> int:
+    tile = tile or moe_tile_rows()
+    tiles = pairs // tile + experts
+    return experts + 1 + (tiles * tile + pairs if padded else pairs) + 2 * tiles + 1
+
+
+def moe_gather(x: torch.Tensor, lists, tile: int, top: int, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[sorted[r] // top] for the rows of the used tiles of a padded layout (zeros where
+    no pair owns the row); bfloat16, rows of 16-byte multiples."""
+    _need(x, torch.bfloat16, "x", contiguous=False)
+    _need(out, torch.bfloat16, "out")
+    _, order, _, _, meta, _ = lists
+    rows, k = out.shape
+    if x.shape[1] != k or x.stride(1) != 1 or rows > order.numel():
+        raise KernelError("moe_gather: shapes do not fit")
+    _check(routed().fsie_moe_gather(_ptr(x), x.stride(0), _ptr(order), _ptr(meta), int(tile), int(top),
+                                    _ptr(out), rows, k, _stream()), "moe_gather")
+    return out
 
 
 def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists, pairs: int, top: int,
@@ -1502,7 +1585,7 @@ def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists,
     _need(x, None, "x", contiguous=False)
     _need(weight, x.dtype, "weight")
     _need(out, x.dtype, "out")
-    offsets, order, tile_expert, tile_row0, meta = lists
+    offsets, order, tile_expert, tile_row0, meta = lists[:5]
     experts, rows, k = weight.shape
     n = rows // 2 if gated else rows
     if x.shape[1] != k or x.stride(1) != 1 or out.shape[1] != n or out.shape[0] < pairs or \
@@ -1516,8 +1599,9 @@ def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists,
 
 
 def moe_combine(expert_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
-                out: torch.Tensor, top: int) -> torch.Tensor:
-    """out[t] = sum_j weights[t, j] * expert_out[t * top + j] (+ shared[t]), summed in 32-bit."""
+                out: torch.Tensor, top: int, place: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = sum_j weights[t, j] * expert_out[t * top + j] (+ shared[t]), summed in 32-bit; with
+    `place` (int32 [tokens * top]) pair p's row of expert_out is place[p]."""
     _need(expert_out, None, "expert_out")
     _need(weights, torch.float32, "weights")
     _need(out, expert_out.dtype, "out")
@@ -1528,6 +1612,8 @@ def moe_combine(expert_out: torch.Tensor, weights: torch.Tensor, shared: Optiona
             raise KernelError("moe_combine: the shared expert's output is not of out's shape")
     if expert_out.numel() < tokens * top * width or weights.numel() < tokens * top:
         raise KernelError("moe_combine: shapes do not fit")
-    _check(routed().fsie_moe_combine(_ptr(expert_out), _ptr(weights), _ptr(shared), _ptr(out), tokens,
-                                     width, int(top), _tag(out.dtype), _stream()), "moe_combine")
+    if place is not None:
+        _need(place, torch.int32, "place")
+    _check(routed().fsie_moe_combine(_ptr(expert_out), _ptr(weights), _ptr(shared), _ptr(place), _ptr(out),
+                                     tokens, width, int(top), _tag(out.dtype), _stream()), "moe_combine")
     return out

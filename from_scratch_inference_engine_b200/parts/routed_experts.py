@@ -26,11 +26,17 @@ class RoutedExperts(Part):
     plus - with `shared` (any feed-forward part) - what that part gives for the token.
 
     All experts' matrices are stacked at bind ([experts, 2 ff, width] gate rows then up rows;
-    [experts, width, ff]).  A step sorts its (token, choice) pairs by expert on the device and runs
-    the two products over tiles of rows that share an expert, so it launches the same kernels
-    whatever the router says.  `names` gives the tensor names below the prefix ("expert" takes the
+    [experts, width, ff]).  The router's logits are a product with a 32-bit result.  A step sorts
+    its (token, choice) pairs by expert on the device and runs the two products over tiles of rows
+    that share an expert, so it launches the same kernels whatever the router says: tiles of 64
+    rows through the mma.sync / FFMA kernels, or - bfloat16 steps with at least `GROUPED_MIN_ROWS`
+    rows per expert on average - the tokens' rows gathered into a layout in which every expert's
+    rows start on a multiple of 256, and the grouped form of the tiled tcgen05 product (SwiGLU in
+    its epilogue) over it.  `names` gives the tensor names below the prefix ("expert" takes the
     expert's index).
     """
+
+    GROUPED_MIN_ROWS = 32       # average rows per expert from which the tcgen05 form is taken
 
     NAMES = {"expert": "e{index}.", "gate": "gate", "up": "up", "down": "down", "router": "router",
              "correction": "correction", "shared": "shared."}
@@ -73,7 +79,7 @@ class RoutedExperts(Part):
         for e in range(self.experts):
             specs += [TensorSpec(self._expert(e, "gate"), (f, h)), TensorSpec(self._expert(e, "up"), (f, h)),
                       TensorSpec(self._expert(e, "down"), (h, f))]
-        specs.append(TensorSpec(self.prefix + self.names["router"], (self.experts, h)))
+        specs.append(TensorSpec(self.prefix + self.names["router"], (self.experts, h)))     # in the compute dtype
         if self.has_correction:
             specs.append(TensorSpec(self.prefix + self.names["correction"], (self.experts,), role="vector"))
         if self.shared is not None:
@@ -87,11 +93,18 @@ class RoutedExperts(Part):
                                       for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")]
                                    for e in range(self.experts)]).contiguous()
-        self.w_router = tensors[self.prefix + self.names["router"]].to(torch.float32).contiguous()
+        self.w_router = tensors[self.prefix + self.names["router"]].contiguous()
+        self._grouped = None             # descriptors of the stacked matrices, made when first needed
         if self.has_correction:
             self.correction = tensors[self.prefix + self.names["correction"]].to(torch.float32).contiguous()
         if self.shared is not None:
             self.shared.bind(tensors, runtime)
+
+    def _grouped_weights(self):
+        if self._grouped is None:
+            self._grouped = (ops.GroupedTiledWeight(self.w_gate_up, True, self.activation),
+                             ops.GroupedTiledWeight(self.w_down, False))
+        return self._grouped
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
         rt = self.runtime
@@ -99,8 +112,29 @@ class RoutedExperts(Part):
         pairs = tokens * top
         ids = rt.buffer("routed.ids", tokens, top, torch.int32)
         weights = rt.buffer("routed.weights", tokens, top, torch.float32)
-        ops.moe_route(y, self.w_router, self.correction, ids, weights, top, self.groups, self.keep,
-                      self.scale, self.scores, self.normalise)
+        logits = rt.linear_f32_out(y, self.w_router, "routed.logits")
+        ops.moe_route(None, None, self.correction, ids, weights, top, self.groups, self.keep,
+                      self.scale, self.scores, self.normalise, logits=logits)
+        shared = None if self.shared is None else self.shared.forward(ctx, y)
+        out = rt.buffer("routed.out", tokens, self.hidden_size, y.dtype)
+        grouped = (y.dtype is torch.bfloat16 and rt.products == "own"
+                   and pairs >= self.GROUPED_MIN_ROWS * self.experts
+                   and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0
+                   and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
+        if grouped:
+            tile = ops.GEMM_TILES_ROWS
+            rows = (pairs // tile + self.experts) * tile
+            lists = ops.moe_align(ids, pairs, self.experts,
+                                  rt.buffer("routed.lists", 1, ops.moe_lists_size(pairs, self.experts, tile, True),
+                                            torch.int32).view(-1), tile, True)
+            gate_up, down = self._grouped_weights()
+            x_sorted = ops.moe_gather(y, lists, tile, top,
+                                      rt.buffer("routed.x_sorted", rows, self.hidden_size, y.dtype))
+            act = rt.buffer("routed.act", rows, self.intermediate_size, y.dtype)
+            ops.gemm_tiles_grouped(gate_up, x_sorted, act, lists[2], lists[4], ctx.error, rt.sm_count)
+            expert_out = rt.buffer("routed.expert_out", rows, self.hidden_size, y.dtype)
+            ops.gemm_tiles_grouped(down, act, expert_out, lists[2], lists[4], ctx.error, rt.sm_count)
+            return ops.moe_combine(expert_out, weights, shared, out, top, place=lists[5])
         lists = ops.moe_align(ids, pairs, self.experts,
                               rt.buffer("routed.lists", 1, ops.moe_lists_size(pairs, self.experts),
                                         torch.int32).view(-1))
@@ -108,6 +142,4 @@ class RoutedExperts(Part):
         ops.moe_product(y, self.w_gate_up, act, lists, pairs, top, True, self.activation)
         expert_out = rt.buffer("routed.expert_out", pairs, self.hidden_size, y.dtype)
         ops.moe_product(act, self.w_down, expert_out, lists, pairs, top, False)
-        shared = None if self.shared is None else self.shared.forward(ctx, y)
-        out = rt.buffer("routed.out", tokens, self.hidden_size, y.dtype)
         return ops.moe_combine(expert_out, weights, shared, out, top)
