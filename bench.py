@@ -515,7 +515,7 @@ def hybrid_workload(args, design="metulix") -> int:
                                "talking_attention_mma", "norm_add_norm", "gated_act", "mingru_scan",
                                "scaled_attention", "rotate_mix_write", "latent_prep", "head_product",
                                "sum_layernorm", "settle_concat", "logit_cap", "sigmoid_gate", "moe_route",
-                               "moe_align", "moe_product", "moe_combine")
+                               "moe_align", "moe_gather", "moe_product", "gemm_tiles_grouped", "moe_combine")
              if hasattr(ops, name)]
 
     def by_kind(fn):

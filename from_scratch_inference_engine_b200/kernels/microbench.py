@@ -4,7 +4,8 @@
 
 KERNEL: attention_decode, attention_prefill, add_rmsnorm, rope_kv_write, swiglu, argmax,
 sample, linear (the library product as the engine calls it), gemm_f32, gemm_decode,
-gemm_decode_swiglu, gemm_tiles, gemm_tiles_swiglu (the engine's own tcgen05 products).
+gemm_decode_swiglu, gemm_tiles, gemm_tiles_swiglu (the engine's own tcgen05 products),
+sum_layernorm, routed_experts (every kernel of a feed-forward of routed experts, one line for all).
 
 Each kernel is timed with CUDA events over --iters launches after --warmup launches; between
 launches a buffer larger than L2 is read so that inputs come from HBM (read, not written:
@@ -166,6 +167,80 @@ def run_attention(args, timer, decode: bool):
     return ms, io_bytes, flops, extra
 
 
+def run_routed_experts(args, timer, dtype):
+    """Every kernel of a feed-forward of routed experts at --tokens, --hidden, --inter (an expert's
+    width), --experts, --top, --groups, --keep with a random router: ms, and the share of the
+    measured peak that the work a token asks for (no padding rows counted) reaches.  Steps with at
+    least 32 rows per expert take the grouped tcgen05 products, others the tiles of 64 rows."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rand = lambda *shape: torch.randn(shape, generator=g, device="cuda", dtype=torch.float32)
+    elem = 2 if dtype is torch.bfloat16 else 4
+    tokens, h, f, experts, top = args.tokens, args.hidden, args.inter, args.experts, args.top
+    pairs = tokens * top
+    y = rand(tokens, h).to(dtype)
+    w_router = (rand(experts, h) / math.sqrt(h)).to(dtype)
+    w_gu = (rand(experts, 2 * f, h) / math.sqrt(h)).to(dtype)
+    w_d = (rand(experts, h, f) / math.sqrt(f)).to(dtype)
+    correction = rand(experts) * 0.1
+    ids = torch.zeros(tokens, top, dtype=torch.int32, device="cuda")
+    weights = torch.zeros(tokens, top, device="cuda")
+    logits = torch.nn.functional.linear(y, w_router).float()
+    peak = peaks()
+    rows = []
+
+    def note(name, ms, nbytes, flops):
+        gbs, tflops = nbytes / (ms * 1e-3) / 1e9, flops / (ms * 1e-3) / 1e12
+        rows.append({"kernel": name, "ms": round(ms, 5), "GB/s": round(gbs, 1), "TFLOP/s": round(tflops, 2),
+                     "frac_hbm": round(gbs / peak["hbm_gbs"], 3), "frac_bf16": round(tflops / peak["bf16_tflops"], 3)})
+
+    note("moe_route", timer(lambda: ops.moe_route(None, None, correction, ids, weights, top, args.groups,
+                                                  args.keep, 2.5, logits=logits)),
+         tokens * (experts * 4 + top * 8), 0.0)
+    used = int(torch.unique(ids).numel())
+    shared = rand(tokens, h).to(dtype)
+    out = torch.empty(tokens, h, dtype=dtype, device="cuda")
+    error = torch.zeros(1, dtype=torch.int32, device="cuda")
+    grouped = dtype is torch.bfloat16 and pairs >= 32 * experts and not args.no_grouped
+    if grouped:
+        tile = ops.GEMM_TILES_ROWS
+        room = (pairs // tile + experts) * tile
+        buffer = torch.zeros(ops.moe_lists_size(pairs, experts, tile, True), dtype=torch.int32, device="cuda")
+        lists = ops.moe_align(ids, pairs, experts, buffer, tile, True)
+        note("moe_align", timer(lambda: ops.moe_align(ids, pairs, experts, buffer, tile, True)), pairs * 12, 0.0)
+        padded = int(lists[4].item()) * tile
+        x_sorted = torch.empty(room, h, dtype=dtype, device="cuda")
+        note("moe_gather", timer(lambda: ops.moe_gather(y, lists, tile, top, x_sorted)),
+             (tokens + pairs) * h * elem, 0.0)
+        gate_up, down = ops.GroupedTiledWeight(w_gu, True, "silu"), ops.GroupedTiledWeight(w_d, False)
+        act = torch.empty(room, f, dtype=dtype, device="cuda")
+        sms = torch.cuda.get_device_properties(0).multi_processor_count
+        note("gemm_tiles_grouped gate,up", timer(lambda: ops.gemm_tiles_grouped(gate_up, x_sorted, act, lists[2], lists[4], error, sms)),
+             (used * 2 * f * h + pairs * (h + f)) * elem, 2.0 * pairs * 2 * f * h)
+        expert_out = torch.empty(room, h, dtype=dtype, device="cuda")
+        note("gemm_tiles_grouped down", timer(lambda: ops.gemm_tiles_grouped(down, act, expert_out, lists[2], lists[4], error, sms)),
+             (used * f * h + pairs * (h + f)) * elem, 2.0 * pairs * f * h)
+        note("moe_combine", timer(lambda: ops.moe_combine(expert_out, weights, shared, out, top, place=lists[5])),
+             (pairs + 2 * tokens) * h * elem, 2.0 * pairs * h)
+        extra = {"rows_with_padding": padded}
+    else:
+        buffer = torch.zeros(ops.moe_lists_size(pairs, experts), dtype=torch.int32, device="cuda")
+        lists = ops.moe_align(ids, pairs, experts, buffer)
+        note("moe_align", timer(lambda: ops.moe_align(ids, pairs, experts, buffer)), pairs * 8, 0.0)
+        act = torch.empty(pairs, f, dtype=dtype, device="cuda")
+        note("moe_product gate,up", timer(lambda: ops.moe_product(y, w_gu, act, lists, pairs, top, True, "silu")),
+             (used * 2 * f * h + tokens * h + pairs * f) * elem, 2.0 * pairs * 2 * f * h)
+        expert_out = torch.empty(pairs, h, dtype=dtype, device="cuda")
+        note("moe_product down", timer(lambda: ops.moe_product(act, w_d, expert_out, lists, pairs, top, False)),
+             (used * f * h + pairs * (h + f)) * elem, 2.0 * pairs * f * h)
+        note("moe_combine", timer(lambda: ops.moe_combine(expert_out, weights, shared, out, top)),
+             (pairs + 2 * tokens) * h * elem, 2.0 * pairs * h)
+        extra = {}
+    print(json.dumps(dict({"kernel": "routed_experts", "dtype": args.dtype, "tokens": tokens, "hidden": h,
+                           "inter": f, "experts": experts, "top": top, "groups": [args.groups, args.keep],
+                           "experts_used": used, "error": int(error.item()), "peaks": peak["source"],
+                           "kernels": rows}, **extra)))
+
+
 def run(args):
     timer = Timer(args.warmup, args.iters, not args.no_flush)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -258,6 +333,15 @@ def run(args):
             elem = 4
             extra = {"frac_ffma": round(2.0 * m * n * k / (ms * 1e-3) / 74.4e12, 3), "f32_kind": args.f32_kind}
         nbytes, flops = (m * k + n * k + m * n) * elem, 2.0 * m * n * k
+    elif args.kernel == "routed_experts":
+        return run_routed_experts(args, timer, dtype)
+    elif args.kernel == "sum_layernorm":
+        x, d1, d2 = rand(args.tokens, args.hidden), rand(args.tokens, args.hidden).to(dtype), \
+            rand(args.tokens, args.hidden).to(dtype)
+        gain, bias = rand(args.hidden), rand(args.hidden)
+        y = torch.empty((args.tokens, args.hidden), dtype=dtype, device="cuda")
+        ms = timer(lambda: ops.sum_layernorm(x, [d1, d2], gain, bias, 1e-6, y))
+        nbytes, flops = args.tokens * args.hidden * (8 + 3 * elem), 8.0 * args.tokens * args.hidden
     else:
         raise SystemExit(f"unknown kernel {args.kernel}")
     peak = peaks()
@@ -290,6 +374,12 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
+    parser.add_argument("--experts", type=int, default=64)
+    parser.add_argument("--top", type=int, default=6)
+    parser.add_argument("--groups", type=int, default=8)
+    parser.add_argument("--keep", type=int, default=4)
+    parser.add_argument("--no-grouped", action="store_true",
+                        help="routed_experts: tiles of 64 rows also where the grouped products would run")
     parser.add_argument("--variant", default="mma", choices=["mma", "tc", "rows16", "whole_tiles"],
                         help="bfloat16 attention: mma.sync with cp.async loads, or tcgen05; float32 "
                              "attention: rows16 takes the kernel for tiles of up to 16 rows; gemm_tiles: "

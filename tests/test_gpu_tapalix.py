@@ -190,7 +190,7 @@ def test_latent_rows_with_pairs_half_a_rotation_apart(dtype, stretched):
 
 
 @pytest.mark.parametrize("experts,top,groups,keep,width", [
-    (12, 4, 3, 2, 64), (6, 2, 6, 3, 40), (8, 3, 1, 1, 36), (64, 6, 8, 3, 256), (5, 5, 1, 1, 20),
+    (15, 4, 3, 2, 64), (6, 2, 6, 3, 40), (8, 3, 1, 1, 36), (64, 6, 8, 3, 256), (5, 5, 1, 1, 20),
     (40, 1, 4, 1, 100), (16, 4, 16, 4, 72)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_router_choice_and_weights(experts, top, groups, keep, width, dtype):
