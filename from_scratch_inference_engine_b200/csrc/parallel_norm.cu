@@ -14,12 +14,15 @@
 
 namespace fsie {
 
-template <typename T>
+// VEC: the width is a multiple of 8 and every row starts on 16 bytes: eight columns per thread and
+// trip, 16-byte accesses (32 bytes of x as two).  The sums run over the same values in another
+// order of the threads' partial sums.
+template <typename T, bool VEC>
 __global__ void sum_layernorm_kernel(float* __restrict__ x, const T* __restrict__ d1,
                                      const T* __restrict__ d2, const float* __restrict__ gain,
                                      const float* __restrict__ bias, const int* __restrict__ rows,
                                      T* __restrict__ y, int width, float eps, int write_x) {
-    extern __shared__ float row_cache[];
+    extern __shared__ __align__(16) float row_cache[];
     __shared__ float scratch[32];
     grid_dependency_wait();
     grid_dependents_go();
@@ -28,33 +31,67 @@ __global__ void sum_layernorm_kernel(float* __restrict__ x, const T* __restrict_
     float* xr = x + s * width;
     const T* a = d1 ? d1 + s * width : nullptr;
     const T* b = d2 ? d2 + s * width : nullptr;
+    constexpr int STEP = VEC ? 8 : 1;
     float sum = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = xr[c];
-        if (a && b) v += to_float(a[c]) + to_float(b[c]);
-        else if (a) v += to_float(a[c]);
-        else if (b) v += to_float(b[c]);
-        if (write_x && (a || b)) xr[c] = v;
-        row_cache[c] = v;
-        sum += v;
+    for (int c = threadIdx.x * STEP; c < width; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], u[8], w[8];
+            load8(xr + c, v);
+            if (a) load8(a + c, u);
+            if (b) load8(b + c, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (a && b) v[i] += u[i] + w[i];
+                else if (a) v[i] += u[i];
+                else if (b) v[i] += w[i];
+                sum += v[i];
+            }
+            if (write_x && (a || b)) store8(xr + c, v);
+            store8(row_cache + c, v);
+        } else {
+            float v = xr[c];
+            if (a && b) v += to_float(a[c]) + to_float(b[c]);
+            else if (a) v += to_float(a[c]);
+            else if (b) v += to_float(b[c]);
+            if (write_x && (a || b)) xr[c] = v;
+            row_cache[c] = v;
+            sum += v;
+        }
     }
     if (!y) return;
+    // every thread reads back only what it wrote itself: no barrier is needed before these loops
     const float mean = block_sum(sum, scratch) / (float)width;
     float sq = 0.f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float d = row_cache[c] - mean;
-        sq += d * d;
+    for (int c = threadIdx.x * STEP; c < width; c += blockDim.x * STEP) {
+#pragma unroll
+        for (int i = 0; i < STEP; ++i) {
+            const float d = row_cache[c + i] - mean;
+            sq += d * d;
+        }
     }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
     T* yr = y + (size_t)r * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = (row_cache[c] - mean) * inv * gain[c];
-        if (bias) v += bias[c];
-        yr[c] = from_float<T>(v);
+    for (int c = threadIdx.x * STEP; c < width; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], g[8], o[8];
+            load8(row_cache + c, v);
+            load8(gain + c, g);
+            if (bias) load8(bias + c, o);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                v[i] = (v[i] - mean) * inv * g[i];
+                if (bias) v[i] += o[i];
+            }
+            store8(yr + c, v);
+        } else {
+            float v = (row_cache[c] - mean) * inv * gain[c];
+            if (bias) v += bias[c];
+            yr[c] = from_float<T>(v);
+        }
     }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void settle_concat_kernel(const float* __restrict__ x, const T* __restrict__ d1,
                                      const T* __restrict__ d2, const float* __restrict__ x0,
                                      T* __restrict__ out, int width) {
@@ -66,13 +103,30 @@ __global__ void settle_concat_kernel(const float* __restrict__ x, const T* __res
     const T* a = d1 ? d1 + t * width : nullptr;
     const T* b = d2 ? d2 + t * width : nullptr;
     T* o = out + t * 2 * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = xr[c];
-        if (a && b) v += to_float(a[c]) + to_float(b[c]);
-        else if (a) v += to_float(a[c]);
-        else if (b) v += to_float(b[c]);
-        o[c] = from_float<T>(v);
-        o[width + c] = from_float<T>(er[c]);
+    constexpr int STEP = VEC ? 8 : 1;
+    for (int c = threadIdx.x * STEP; c < width; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], u[8], w[8];
+            load8(xr + c, v);
+            if (a) load8(a + c, u);
+            if (b) load8(b + c, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (a && b) v[i] += u[i] + w[i];
+                else if (a) v[i] += u[i];
+                else if (b) v[i] += w[i];
+            }
+            store8(o + c, v);
+            load8(er + c, v);
+            store8(o + width + c, v);
+        } else {
+            float v = xr[c];
+            if (a && b) v += to_float(a[c]) + to_float(b[c]);
+            else if (a) v += to_float(a[c]);
+            else if (b) v += to_float(b[c]);
+            o[c] = from_float<T>(v);
+            o[width + c] = from_float<T>(er[c]);
+        }
     }
 }
 
@@ -86,7 +140,7 @@ __global__ void logit_cap_kernel(float* __restrict__ z, long long count, float s
     }
 }
 
-template <typename T>
+template <typename T, bool VEC>
 __global__ void sigmoid_gate_kernel(T* __restrict__ out, int out_ld, const T* __restrict__ g, int g_ld,
                                     int width) {
     grid_dependency_wait();
@@ -94,15 +148,33 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ out, int out_ld, const T* __
     const size_t t = blockIdx.x;
     T* o = out + t * out_ld;
     const T* gr = g + t * g_ld;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float gate = 1.0f / (1.0f + expf(-to_float(gr[c])));
-        o[c] = from_float<T>(to_float(o[c]) * gate);
+    constexpr int STEP = VEC ? 8 : 1;
+    for (int c = threadIdx.x * STEP; c < width; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], z[8];
+            load8(o + c, v);
+            load8(gr + c, z);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] *= 1.0f / (1.0f + expf(-z[i]));
+            store8(o + c, v);
+        } else {
+            const float gate = 1.0f / (1.0f + expf(-to_float(gr[c])));
+            o[c] = from_float<T>(to_float(o[c]) * gate);
+        }
     }
 }
 
 }  // namespace fsie
 
 using namespace fsie;
+
+// every pointer given (null ones aside) starts on 16 bytes
+template <typename... P>
+static bool aligned16(P... pointers) {
+    size_t bits = 0;
+    ((bits |= reinterpret_cast<size_t>(pointers)), ...);
+    return (bits & 15) == 0;
+}
 
 extern "C" {
 
@@ -113,29 +185,31 @@ int fsie_sum_layernorm(float* x, const void* d1, const void* d2, const float* ga
     if (width <= 0 || !x || (y && !gain)) return ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)width * sizeof(float);
     if (smem > 200 * 1024) return ERR_UNSUPPORTED;
-    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-    if (dtype == DTYPE_F32) {
-        if (smem > 48 * 1024)
-            cudaFuncSetAttribute(sum_layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return launch_dependent(sum_layernorm_kernel<float>, num_rows, threads, smem, stream, x, (const float*)d1,
-                                (const float*)d2, gain, bias, rows, (float*)y, width, eps, write_x);
-    }
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(sum_layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_dependent(sum_layernorm_kernel<bf16>, num_rows, threads, smem, stream, x, (const bf16*)d1,
-                            (const bf16*)d2, gain, bias, rows, (bf16*)y, width, eps, write_x);
+    const bool vec = width % 8 == 0 && aligned16(x, d1, d2, gain, bias, y);
+    const int threads = vec ? (width >= 4096 ? 512 : (width >= 1024 ? 256 : 128))
+                            : (width >= 2048 ? 512 : (width >= 512 ? 256 : 128));
+#define FSIE_NORM(T, V)                                                                                        \
+    (smem > 48 * 1024 ? (void)cudaFuncSetAttribute(sum_layernorm_kernel<T, V>,                                 \
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)     \
+                      : (void)0,                                                                               \
+     launch_dependent(sum_layernorm_kernel<T, V>, num_rows, threads, smem, stream, x, (const T*)d1, (const T*)d2, \
+                      gain, bias, rows, (T*)y, width, eps, write_x))
+    if (dtype == DTYPE_F32) return vec ? FSIE_NORM(float, true) : FSIE_NORM(float, false);
+    return vec ? FSIE_NORM(bf16, true) : FSIE_NORM(bf16, false);
+#undef FSIE_NORM
 }
 
 int fsie_settle_concat(const float* x, const void* d1, const void* d2, const float* x0, void* out,
                        int tokens, int width, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (width <= 0 || !x || !x0 || !out) return ERR_BAD_ARGUMENT;
-    const int threads = width >= 1024 ? 256 : 128;
-    if (dtype == DTYPE_F32)
-        return launch_dependent(settle_concat_kernel<float>, tokens, threads, 0, stream, x, (const float*)d1,
-                                (const float*)d2, x0, (float*)out, width);
-    return launch_dependent(settle_concat_kernel<bf16>, tokens, threads, 0, stream, x, (const bf16*)d1,
-                            (const bf16*)d2, x0, (bf16*)out, width);
+    const bool vec = width % 8 == 0 && aligned16(x, d1, d2, x0, out);
+    const int threads = vec ? (width >= 2048 ? 256 : 128) : (width >= 1024 ? 256 : 128);
+#define FSIE_CONCAT(T, V) launch_dependent(settle_concat_kernel<T, V>, tokens, threads, 0, stream, x, (const T*)d1, \
+                                           (const T*)d2, x0, (T*)out, width)
+    if (dtype == DTYPE_F32) return vec ? FSIE_CONCAT(float, true) : FSIE_CONCAT(float, false);
+    return vec ? FSIE_CONCAT(bf16, true) : FSIE_CONCAT(bf16, false);
+#undef FSIE_CONCAT
 }
 
 int fsie_logit_cap(float* z, long long count, float scale, float cap, cudaStream_t stream) {
@@ -149,12 +223,13 @@ int fsie_logit_cap(float* z, long long count, float scale, float cap, cudaStream
 int fsie_sigmoid_gate(void* out, int out_ld, const void* g, int g_ld, int tokens, int width, int dtype,
                       cudaStream_t stream) {
     if (tokens <= 0 || width <= 0) return 0;
-    const int threads = width >= 1024 ? 256 : 128;
-    if (dtype == DTYPE_F32)
-        return launch_dependent(sigmoid_gate_kernel<float>, tokens, threads, 0, stream, (float*)out, out_ld,
-                                (const float*)g, g_ld, width);
-    return launch_dependent(sigmoid_gate_kernel<bf16>, tokens, threads, 0, stream, (bf16*)out, out_ld,
-                            (const bf16*)g, g_ld, width);
+    const bool vec = width % 8 == 0 && out_ld % 8 == 0 && g_ld % 8 == 0 && aligned16(out, g);
+    const int threads = vec ? (width >= 2048 ? 256 : 128) : (width >= 1024 ? 256 : 128);
+#define FSIE_GATE(T, V) launch_dependent(sigmoid_gate_kernel<T, V>, tokens, threads, 0, stream, (T*)out, out_ld, \
+                                         (const T*)g, g_ld, width)
+    if (dtype == DTYPE_F32) return vec ? FSIE_GATE(float, true) : FSIE_GATE(float, false);
+    return vec ? FSIE_GATE(bf16, true) : FSIE_GATE(bf16, false);
+#undef FSIE_GATE
 }
 
 }  // extern "C"

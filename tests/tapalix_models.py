@@ -67,13 +67,13 @@ CONFIGS = {
     "experts": model(71, 32, 1e-6, [
         with_mlp(gated(1, 8, 8, 8), moe(16, 12, 3, groups=(4, 2), scale=2.5, shared=40))],
         embedding=3.0),
-    # the loop: three passes over the two middle layers, each pass with its own cache
+    # the loop: two passes over the two middle layers, each pass with its own cache
     "loop": model(131, 64, 1e-6, [
         with_mlp(latent(2, 16, 8, 12, 24, scale=0.5, stretch=scaling(2.0, 64, 8.0, 1.0)), moe(32, 6, 2, groups=(3, 2), shared=24)),
         with_mlp(gated(4, 8, 16, 40, scale=0.7), moe(16, 8, 3, groups=(2, 1), scale=2.0, shared=48)),
         with_mlp(latent(4, 8, 4, 8, 40, scale=0.7, base=100.0), None),
         with_mlp(gated(2, 16, 8, 12), moe(40, 4, 1))],
-        loop=(1, 3, 3), embedding=4.0, logit_scale=2.0, softcap=12.0),
+        loop=(1, 3, 2), embedding=4.0, logit_scale=2.5, softcap=12.0),
     # a loop from the first layer on and of a single pass; a loop up to the last layer
     "loop_first": model(90, 40, 1e-5, [
         with_mlp(gated(2, 8, 8, 16), moe(24, 4, 2, groups=(4, 2))),
@@ -92,8 +92,8 @@ CONFIGS = {
     "wide": model(150, 128, 1e-6, [
         with_mlp(latent(8, 32, 16, 32, 64, stretch=scaling(2.0, 128, 16.0, 1.0)), moe(64, 8, 2, groups=(4, 2), scale=1.5, shared=96)),
         with_mlp(gated(4, 64, 64, 128), moe(32, 16, 4, groups=(4, 3), scale=2.0, shared=64)),
-        with_mlp(latent(4, 64, 64, 64, 64, base=1e6), moe(64, 4, 2))],
-        loop=(1, 2, 2), embedding=8.0, logit_scale=1.5, softcap=15.0),
+        with_mlp(latent(4, 64, 64, 64, 64, base=5e5), moe(64, 4, 2))],
+        loop=(1, 2, 2), embedding=8.0, logit_scale=1.5, softcap=14.0),
 }
 
 

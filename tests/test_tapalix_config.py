@@ -20,10 +20,10 @@ def test_every_test_configuration_reads_and_round_trips():
 def test_run_order_repeats_the_looped_stretch_with_caches_of_its_own():
     spec = config_from_dict(tm.CONFIGS["loop"]).build_spec()
     assert [(c.layer, c.inlet) for c in spec.schedule] == \
-        [(0, None), (1, 0), (2, None), (1, 0), (2, None), (1, 0), (2, None), (3, None)]
+        [(0, None), (1, 0), (2, None), (1, 0), (2, None), (3, None)]
     resolved = spec.resolved_schedule()
-    assert [entry for _, entry, _ in resolved] == list(range(8))      # every call its own cache entry
-    assert spec.embedding_scale == 4.0 and spec.logit_scale == 2.0 and spec.logit_softcap == 12.0
+    assert [entry for _, entry, _ in resolved] == list(range(6))      # every call its own cache entry
+    assert spec.embedding_scale == 4.0 and spec.logit_scale == 2.5 and spec.logit_softcap == 12.0
     assert len(spec.inlets) == 1
     first = config_from_dict(tm.CONFIGS["loop_first"]).build_spec()
     assert [(c.layer, c.inlet) for c in first.schedule] == [(0, 0), (1, None)]
@@ -55,10 +55,10 @@ def test_cache_needs_follow_the_mixers():
     from from_scratch_inference_engine_b200.parts.model import DecoderModel
     model = DecoderModel(config_from_dict(tm.CONFIGS["loop"]).build_spec())
     needs = model.cache_needs()
-    assert len(needs) == 8
+    assert len(needs) == 6
     assert (needs[0].head_dim, needs[0].value_dim, needs[0].values_in_keys) == (32, 24, True)
     assert (needs[1].head_dim, needs[1].value_dim) == (40, 40)          # no turned part beside the latent
-    assert needs[1] == needs[3] == needs[5] and needs[2] == needs[4] == needs[6]
+    assert needs[1] == needs[3] and needs[2] == needs[4]
     assert all(need.window == 0 for need in needs)
     assert all(state is None for state in model.state_needs())
 
