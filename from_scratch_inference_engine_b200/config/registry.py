@@ -13,6 +13,7 @@ import json
 from pathlib import Path
 from typing import Any, Dict, Mapping, Type
 
+from .kufulix import KufulixConfig
 from .metulix import MetulixConfig
 from .qwen2 import ConfigError, Qwen2Config
 from .tapalix import TapalixConfig
@@ -82,3 +83,4 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config, model_type="qwen2")
 register_architecture("Metulix", MetulixConfig)
 register_architecture("Zadepel", ZadepelConfig)
 register_architecture("Tapalix", TapalixConfig)
+register_architecture("Kufulix", KufulixConfig)

@@ -87,6 +87,8 @@ class ModelSpec:
     logit_scale: float = 1.0               # logits = head(x) * logit_scale ...
     logit_softcap: float = 0.0             # ... then cap * tanh(logits / cap) (0: no cap)
     inlets: Tuple[Tuple[PartSpec, str], ...] = ()      # (part, tensor-name prefix) per inlet
+    embedding_norm: Optional[PartSpec] = None          # a norm on the embedding rows: its result is
+    embedding_norm_prefix: str = ""                    # the residual stream the first layer meets
 
     def resolved_schedule(self) -> List[Tuple[int, int, bool]]:
         """(layer, cache entry, writes) per call with defaults filled in and checked."""

@@ -42,10 +42,13 @@ LIBRARIES: Dict[str, Sequence[str]] = {
     "gemm_tiles": ("gemm_tiles_tcgen05.cu",),
     # mma.sync product without set-up for steps of few tokens against small matrices
     "gemm_skinny": ("gemm_skinny.cu",),
-    # parts of hybrid decoders: layer norm on a sublayer's output, decaying linear attention over
-    # per-request state, and windowed attention with mixed heads behind a short convolution
-    "hybrid": ("layernorm.cu", "lightning.cu", "talking_attention.cu", "talking_attention_bf16.cu",
+    # parts of hybrid decoders: layer norm on a sublayer's output, and windowed attention with mixed
+    # heads behind a short convolution
+    "hybrid": ("layernorm.cu", "talking_attention.cu", "talking_attention_bf16.cu",
                "talking_attention_f32.cu", "talking_attention_mma.cu"),
+    # recurrences over per-request state of the form S <- a S + k v^T, o = S^T q: decaying linear
+    # attention, and a state-space mixer with its convolution, step sizes and gated norm
+    "scan": ("lightning.cu", "ssd.cu"),
     # more parts: RMS norms on both sides of a sublayer, gated activations, the minGRU recurrence,
     # attention with a scale per head and keys and values of different widths, attention over a
     # cache of latent rows

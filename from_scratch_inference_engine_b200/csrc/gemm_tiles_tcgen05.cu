@@ -73,7 +73,7 @@ struct TileGemmParams {
     const bf16* bias;               // [N] or null
     int M, N, K;                    // N = output features (SwiGLU: the intermediate size)
     int up_row0;                    // SwiGLU: row of w where the up rows start
-    int gate;                       // gated epilogue: 1 = SiLU on the gate, 2 = GELU (tanh form)
+    int gate;                       // gated epilogue: 1 = SiLU on the gate, 2 = GELU (tanh form); plain epilogue: 3 = the square of relu on the result
     int m_tiles, n_tiles;
     int out_f32;
     int tma_store;                  // y is written through map_y (bf16, rows on 16-byte boundaries)
@@ -501,6 +501,13 @@ gemm_tiles_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_consta
 #pragma unroll
                         for (int j = 0; j < 32; ++j) if (n + j < p.N) v[j] += __bfloat162float(p.bias[n + j]);
                     }
+                    if (p.gate == 3) {      // no gate, the square of relu: on the value as bfloat16 would store it
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float r = fmaxf(__bfloat162float(__float2bfloat16_rn(v[j])), 0.f);
+                            v[j] = r * r;
+                        }
+                    }
                 }
                 if (!p.tma_store) {
                     store_row_chunk(p, row0 + lane, n, v, vector_ok);
@@ -725,7 +732,8 @@ int fsie_gemm_tiles_workspace(int M, int N, int K, int swiglu, int blocks, long 
 }
 
 // y[M, N] = x[M, K] * w^T (+ bias), or for swiglu != 0 y[M, N] = act(x w_gate^T) * (x w_up^T) with
-// w = [gate rows (N); up rows (N)] and act = SiLU (swiglu = 1) or the tanh form of GELU (2).  `blocks` is the size of the persistent grid (the number
+// w = [gate rows (N); up rows (N)] and act = SiLU (swiglu = 1) or the tanh form of GELU (2); swiglu = 3: no gate,
+// y = relu(x w^T)^2 on the product as bfloat16 would store it.  `blocks` is the size of the persistent grid (the number
 // of SMs; it is cut to the pairs that can run at once and to the number of tiles).  workspace and
 // counters: see fsie_gemm_tiles_workspace; with less than that (or null) every tile is summed by
 // one pair, as if the last round were full.
@@ -733,8 +741,9 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
                     int M, int N, int K, int swiglu, int out_f32, int blocks, float* workspace,
                     long long workspace_floats, int* counters, int counters_len, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || (swiglu && out_f32) || swiglu < 0 || swiglu > 2)
+    if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || (swiglu && out_f32) || swiglu < 0 || swiglu > 3)
         return ERR_BAD_ARGUMENT;
+    const int gated = swiglu == 1 || swiglu == 2;
     CUtensorMap map_w, map_x;
     memcpy(&map_w, weight_map, sizeof(map_w));
     int rc = make_map(&map_x, x, M, K, ldx);
@@ -742,7 +751,7 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
     TileGemmParams p;
     int pairs = 0, need_counters = 0;
     long long need_floats = 0;
-    rc = plan(M, N, K, swiglu, blocks, p, &pairs, &need_floats, &need_counters);
+    rc = plan(M, N, K, gated, blocks, p, &pairs, &need_floats, &need_counters);
     if (rc != 0) return rc;
     if (p.share_pairs > 0 && (!workspace || !counters || workspace_floats < need_floats || counters_len < need_counters))
         p.share_pairs = 0;
@@ -757,7 +766,7 @@ int fsie_gemm_tiles(const void* weight_map, const void* x, long long ldx, void* 
         rc = make_out_map(&map_y, y, M, N, ldy);
         if (rc != 0) return rc;
     }
-    return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
+    return gated ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
 }
 
 // The grouped form: the rows of x [M, K] were sorted by group, every group's rows start on a
@@ -772,8 +781,9 @@ int fsie_gemm_tiles_grouped(const void* weight_map, const void* x, long long ldx
                             const int* tiles_used, int group_rows, int* error, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || blocks <= 0 || swiglu < 0 ||
-        swiglu > 2 || M % TILE != 0 || !tile_group || !tiles_used || group_rows <= 0)
+        swiglu > 3 || M % TILE != 0 || !tile_group || !tiles_used || group_rows <= 0)
         return ERR_BAD_ARGUMENT;
+    const int gated = swiglu == 1 || swiglu == 2;
     CUtensorMap map_w, map_x;
     memcpy(&map_w, weight_map, sizeof(map_w));
     int rc = make_map(&map_x, x, M, K, ldx);
@@ -781,7 +791,7 @@ int fsie_gemm_tiles_grouped(const void* weight_map, const void* x, long long ldx
     TileGemmParams p;
     int pairs = 0, need_counters = 0;
     long long need_floats = 0;
-    rc = plan(M, N, K, swiglu, blocks, p, &pairs, &need_floats, &need_counters);
+    rc = plan(M, N, K, gated, blocks, p, &pairs, &need_floats, &need_counters);
     if (rc != 0) return rc;
     p.share_pairs = 0;          // how many tiles there are is known on the device only: no tile is shared
     p.workspace = nullptr; p.counters = nullptr;
@@ -794,7 +804,7 @@ int fsie_gemm_tiles_grouped(const void* weight_map, const void* x, long long ldx
         rc = make_out_map(&map_y, y, M, N, ldy);
         if (rc != 0) return rc;
     }
-    return swiglu ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
+    return gated ? launch<EPI_SWIGLU>(map_w, map_x, map_y, p, pairs, stream) : launch<EPI_PLAIN>(map_w, map_x, map_y, p, pairs, stream);
 }
 
 }  // extern "C"

@@ -9,6 +9,12 @@
 // sequence, so the result does not depend on how the tokens were cut into steps beyond rounding
 // (long prompts sum chunk by chunk).  The activations, the decay, the state and the output o are
 // 32-bit whatever the storage type.
+//
+// The scan also serves recurrences of the same form with a decay per token and head (`decay_tok`
+// [tokens, heads] in place of the constant per head) and with q and k columns that `share` heads
+// read together (head h reads the q and k of column group h / share): a state-space mixer's
+// S_t = a_t S_(t-1) + B_t (dt_t x_t)^T, o_t = S_t^T C_t.  A request's state starts `state_stride`
+// floats after the one before it (a slot may hold more than S).
 #include "common.cuh"
 
 namespace fsie {
@@ -44,12 +50,14 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
                       const int* __restrict__ item_slots, float* __restrict__ state,
                       const float* __restrict__ decay, float* __restrict__ out, int heads, int dim,
                       int vdim, const int* __restrict__ seg_item, const int* __restrict__ seg_row0,
-                      int seg_tokens, float* __restrict__ chunk_states, int phase) {
+                      int seg_tokens, float* __restrict__ chunk_states, int phase, int share,
+                      const float* __restrict__ decay_tok, long long state_stride) {
     constexpr int PAD = DR >= 4 ? DR + 4 : DR;
     constexpr int ROW_LEN = SCAN_ROW_GROUPS * PAD;
     __shared__ __align__(16) float qs[SCAN_TOKENS * ROW_LEN];
     __shared__ __align__(16) float ks[SCAN_TOKENS * ROW_LEN];
     __shared__ __align__(16) float vs[SCAN_TOKENS * SCAN_COLS];
+    __shared__ float ls[SCAN_TOKENS];                  // the decay of each staged token
     grid_dependency_wait();
     grid_dependents_go();
     const int item = seg_item ? seg_item[blockIdx.z] : blockIdx.z, head = blockIdx.y;
@@ -63,12 +71,13 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
     const bool from_zero = phase == 1, write_out = phase != 1;
     const int rg = threadIdx.x & (SCAN_ROW_GROUPS - 1), cg = threadIdx.x / SCAN_ROW_GROUPS;
     const int col0 = blockIdx.x * SCAN_COLS + cg * 4;
-    const bool wide = (vdim & 3) == 0;                 // rows of the state start on 16 bytes
+    const bool wide = (vdim & 3) == 0 && (state_stride & 3) == 0;                 // rows of the state start on 16 bytes
     // q and k rows of a head start on 16 bytes and end on them: staged four values at a time
     const bool vec = DR * SCAN_ROW_GROUPS >= 4 && ((dim | ld | q_off | k_off) & 3) == 0;
-    float* mine = (phase == 0 ? state + (((size_t)slot * heads + head) * dim) * vdim
+    float* mine = (phase == 0 ? state + (size_t)slot * state_stride + ((size_t)head * dim) * vdim
                               : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim);
-    const float lambda = decay[head];
+    const float head_decay = decay ? decay[head] : 1.f;
+    const int qk_head = head / share;                  // `share` heads read the same q and k columns
     float s[DR][4];
 #pragma unroll
     for (int i = 0; i < DR; ++i) {
@@ -91,7 +100,7 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
             constexpr int CHUNKS = SCAN_ROW_GROUPS * DR / 4 > 0 ? SCAN_ROW_GROUPS * DR / 4 : 1;
             for (int idx = threadIdx.x; idx < n * CHUNKS; idx += blockDim.x) {
                 const int t = idx / CHUNKS, d = (idx - t * CHUNKS) * 4;
-                const float* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
+                const float* row = proj + (size_t)(start + t0 + t) * ld + qk_head * dim + d;
                 const int at = t * ROW_LEN + scan_row_at<DR>(d);
                 const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
                 if (write_out)
@@ -101,7 +110,7 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
         } else {
             for (int idx = threadIdx.x; idx < n * SCAN_ROW_GROUPS * DR; idx += blockDim.x) {
                 const int t = idx / (SCAN_ROW_GROUPS * DR), d = idx - t * (SCAN_ROW_GROUPS * DR);
-                const float* row = proj + (size_t)(start + t0 + t) * ld + head * dim + d;
+                const float* row = proj + (size_t)(start + t0 + t) * ld + qk_head * dim + d;
                 const int at = t * ROW_LEN + scan_row_at<DR>(d);
                 if (write_out) qs[at] = d < dim ? row[q_off] : 0.f;
                 ks[at] = d < dim ? row[k_off] : 0.f;
@@ -112,8 +121,11 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
             const int cc = blockIdx.x * SCAN_COLS + c;
             vs[idx] = cc < vdim ? proj[(size_t)(start + t0 + t) * ld + v_off + head * vdim + cc] : 0.f;
         }
+        if (threadIdx.x < n)
+            ls[threadIdx.x] = decay_tok ? decay_tok[(size_t)(start + t0 + threadIdx.x) * heads + head] : head_decay;
         __syncthreads();
         for (int t = 0; t < n; ++t) {
+            const float lambda = ls[t];
             const float4 v4 = *reinterpret_cast<const float4*>(vs + t * SCAN_COLS + cg * 4);
             const float v[4] = {v4.x, v4.y, v4.z, v4.w};
             float kk[DR], qq[DR];
@@ -197,10 +209,12 @@ __global__ void silu_rows_kernel(const T* __restrict__ proj, int ld, int width, 
 // tokens from a zero state) becomes the state at the start of chunk c, and the request's slot
 // receives the state after its last chunk.  S_after = decay^len * S_before + sum.  One thread per
 // state element; chunks are listed request by request, in order.
-__global__ void lightning_chain_kernel(const int* __restrict__ item_qlen, const int* __restrict__ item_slots,
+__global__ void lightning_chain_kernel(const int* __restrict__ item_qstart, const int* __restrict__ item_qlen,
+                                       const int* __restrict__ item_slots,
                                        int items, float* __restrict__ state, const float* __restrict__ decay,
                                        float* __restrict__ chunk_states, int seg_tokens, int heads,
-                                       int dim, int vdim) {
+                                       int dim, int vdim, const float* __restrict__ decay_tok,
+                                       long long state_stride) {
     const int item = blockIdx.y;
     const int slot = item_slots[item];
     if (slot < 0) return;
@@ -211,18 +225,21 @@ __global__ void lightning_chain_kernel(const int* __restrict__ item_qlen, const 
     for (int i = 0; i < item; ++i) first += (item_qlen[i] + seg_tokens - 1) / seg_tokens;
     const int count = item_qlen[item];
     const int chunks = (count + seg_tokens - 1) / seg_tokens;
-    const float lambda = decay[e / per_head];
-    float s = state[(size_t)slot * per_state + e];
+    const int head = (int)(e / per_head);
+    const float lambda = decay ? decay[head] : 1.f;
+    const float* per_token = decay_tok ? decay_tok + (size_t)item_qstart[item] * heads + head : nullptr;
+    float s = state[(size_t)slot * state_stride + e];
     for (int c = 0; c < chunks; ++c) {
         const int len = min(seg_tokens, count - c * seg_tokens);
         float* at = chunk_states + (size_t)(first + c) * per_state + e;
         const float sum = *at;
         *at = s;
         float power = 1.f;                                 // decay^len by the same products as the scan
-        for (int t = 0; t < len; ++t) power *= lambda;
+        for (int t = 0; t < len; ++t)
+            power *= per_token ? per_token[(size_t)(c * seg_tokens + t) * heads] : lambda;
         s = power * s + sum;
     }
-    state[(size_t)slot * per_state + e] = s;
+    state[(size_t)slot * state_stride + e] = s;
 }
 
 // One block per token: y = T( o * rsqrt(mean(o^2) + eps) * gain * sigmoid(gate) ).
@@ -275,9 +292,12 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
                         const int* item_qstart, const int* item_qlen, const int* item_slots,
                         int items, float* state, const float* decay, float* out, int heads,
                         int dim, int vdim, const int* seg_item, const int* seg_row0, int num_segs,
-                        int seg_tokens, float* chunk_states, cudaStream_t stream) {
+                        int seg_tokens, float* chunk_states, int share, const float* decay_tok,
+                        long long state_stride, cudaStream_t stream) {
     if (items <= 0) return 0;
-    if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535) return ERR_BAD_ARGUMENT;
+    if (heads <= 0 || dim <= 0 || vdim <= 0 || heads > 65535 || items > 65535 || share <= 0 ||
+        heads % share || (!decay && !decay_tok) || state_stride < (long long)heads * dim * vdim)
+        return ERR_BAD_ARGUMENT;
     if (dim > SCAN_ROW_GROUPS * 16) return ERR_UNSUPPORTED;
     const bool chunked = seg_item != nullptr;
     if (chunked && (!seg_row0 || !chunk_states || num_segs <= 0 || num_segs > 65535 || seg_tokens <= 0))
@@ -290,7 +310,8 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
 #define FSIE_SCAN(T, DPT)                                                                        \
     launch_code = launch_dependent(lightning_scan_kernel<DPT>, grid, threads, 0, stream,         \
         proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
-        decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase)
+        decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase, share, \
+        decay_tok, state_stride)
 #define FSIE_SCAN_BY_SIZE(T)                                                                     \
     do {                                                                                         \
         if (per_thread <= 1) FSIE_SCAN(T, 1);                                                    \
@@ -305,7 +326,8 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
         int code;
         const size_t per_state = (size_t)heads * dim * vdim;
         lightning_chain_kernel<<<dim3((unsigned)((per_state + 255) / 256), items), 256, 0, stream>>>(
-            item_qlen, item_slots, items, state, decay, chunk_states, seg_tokens, heads, dim, vdim);
+            item_qstart, item_qlen, item_slots, items, state, decay, chunk_states, seg_tokens, heads, dim, vdim,
+            decay_tok, state_stride);
         code = FSIE_LAUNCH_CHECK();
         if (code) return code;
         phase = 2;

@@ -47,7 +47,7 @@ __global__ void moe_route_kernel(const T* __restrict__ y, int y_ld, const float*
                                  const float* __restrict__ logits,
                                  const float* __restrict__ correction, int* __restrict__ ids,
                                  float* __restrict__ weights, int width, int experts, int top, int groups,
-                                 int keep, float scale, int softmax_scores, int normalise) {
+                                 int keep, float scale, int softmax_scores, int normalise, int group_max) {
     extern __shared__ float route_smem[];
     float* row = route_smem;                       // [width]
     float* score = row + width;                    // [experts] s
@@ -99,7 +99,7 @@ __global__ void moe_route_kernel(const T* __restrict__ y, int y_ld, const float*
                 if (v > first) { second = first; first = v; }
                 else if (v > second) second = v;
             }
-            group_score[g] = per > 1 ? first + second : first;
+            group_score[g] = (per > 1 && !group_max) ? first + second : first;
             group_taken[g] = 0;
         }
         __syncwarp();
@@ -212,15 +212,17 @@ __global__ void moe_gather_kernel(const bf16* __restrict__ x, long long x_ld, co
 // token = pair / top and written in sorted order.  Not GATED: rows are read in sorted order and
 // written at their pair.
 __device__ __forceinline__ float gate_fn(float g, int kind) {
+    if (kind == 2) { const float r = fmaxf(g, 0.f); return r * r; }      // the square of relu
     if (kind == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     return g / (1.0f + expf(-g));
 }
 
-template <typename T, bool GATED>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(256) moe_product_kernel(
         const T* __restrict__ x, long long x_ld, const T* __restrict__ w, T* __restrict__ out, long long out_ld,
         const int* __restrict__ offsets, const int* __restrict__ sorted, const int* __restrict__ tile_expert,
         const int* __restrict__ tile_row0, const int* __restrict__ meta, int top, int n, int k, int gate_kind) {
+    constexpr bool GATED = MODE == 1, FIRST = MODE != 0;
     __shared__ float xs[16][MOE_TILE + 4];
     __shared__ float ws[16][MOE_TILE + 4];
     __shared__ int src[MOE_TILE], dst[MOE_TILE];
@@ -236,8 +238,8 @@ __global__ void __launch_bounds__(256) moe_product_kernel(
     if (threadIdx.x < MOE_TILE) {
         const int r = threadIdx.x;
         const int pair = r < rows ? sorted[r0 + r] : -1;
-        src[r] = pair < 0 ? -1 : (GATED ? pair / top : r0 + r);
-        dst[r] = pair < 0 ? -1 : (GATED ? r0 + r : pair);
+        src[r] = pair < 0 ? -1 : (FIRST ? pair / top : r0 + r);
+        dst[r] = pair < 0 ? -1 : (FIRST ? r0 + r : pair);
     }
     __syncthreads();
     const T* we = w + (size_t)e * (GATED ? 2 : 1) * n * k;
@@ -292,7 +294,8 @@ __global__ void __launch_bounds__(256) moe_product_kernel(
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const int c = n0 + tx * 4 + j;
-                if (c < n) o[c] = from_float<T>(acc[i][j]);
+                if (c < n) o[c] = MODE == 2 ? from_float<T>(gate_fn(to_float(from_float<T>(acc[i][j])), gate_kind))
+                                            : from_float<T>(acc[i][j]);
             }
         }
     }
@@ -319,12 +322,13 @@ __device__ __forceinline__ void mm_cp16(void* dst, const void* src, bool valid) 
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(mm_smem_u32(dst)), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool GATED>
+template <int MODE>
 __global__ void __launch_bounds__(128) moe_product_mma_kernel(
         const bf16* __restrict__ x, long long x_ld, const bf16* __restrict__ w, bf16* __restrict__ out,
         long long out_ld, const int* __restrict__ offsets, const int* __restrict__ sorted,
         const int* __restrict__ tile_expert, const int* __restrict__ tile_row0, const int* __restrict__ meta,
         int top, int n, int k, int gate_kind) {
+    constexpr bool GATED = MODE == 1, FIRST = MODE != 0;
     __shared__ __align__(16) bf16 xs[2][MOE_TILE][MM_LD];
     __shared__ __align__(16) bf16 ws[2][MOE_TILE][MM_LD];
     __shared__ int src[MOE_TILE], dst[MOE_TILE];
@@ -340,8 +344,8 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(
     const int g = lane >> 2, t = lane & 3;
     if (tid < MOE_TILE) {
         const int pair = tid < rows ? sorted[r0 + tid] : -1;
-        src[tid] = pair < 0 ? -1 : (GATED ? pair / top : r0 + tid);
-        dst[tid] = pair < 0 ? -1 : (GATED ? r0 + tid : pair);
+        src[tid] = pair < 0 ? -1 : (FIRST ? pair / top : r0 + tid);
+        dst[tid] = pair < 0 ? -1 : (FIRST ? r0 + tid : pair);
     }
     __syncthreads();
     const bf16* we = w + (size_t)e * (GATED ? 2 : 1) * n * k;
@@ -414,7 +418,9 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int c = n0 + j * 8 + 2 * t + h;
-                    if (c < n) o[c] = __float2bfloat16_rn(acc[j][2 * i + h]);
+                    if (c < n)
+                        o[c] = MODE == 2 ? __float2bfloat16_rn(gate_fn(__bfloat162float(__float2bfloat16_rn(acc[j][2 * i + h])), gate_kind))
+                                         : __float2bfloat16_rn(acc[j][2 * i + h]);
                 }
             }
         }
@@ -425,17 +431,23 @@ __global__ void __launch_bounds__(128) moe_product_mma_kernel(
 template <typename T, bool VEC>
 __global__ void moe_combine_kernel(const T* __restrict__ expert_out, const float* __restrict__ weights,
                                    const T* __restrict__ shared, const int* __restrict__ place,
-                                   T* __restrict__ out, int width, int top) {
+                                   T* __restrict__ out, int width, int top, const int* __restrict__ ids,
+                                   int experts, const T* __restrict__ y, long long y_ld) {
     grid_dependency_wait();
     grid_dependents_go();
     const size_t t = blockIdx.x;
+    // a choice at or beyond `experts` is an identity expert: its output is the token's input row
     if (VEC) {          // eight columns per thread, 16-byte accesses; the sums run in the same order
         for (int c = threadIdx.x * 8; c < width; c += blockDim.x * 8) {
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f}, v[8];
             for (int j = 0; j < top; ++j) {
-                const size_t row = place ? (size_t)place[t * top + j] : t * top + j;
                 const float w = weights[t * top + j];
-                load8(expert_out + row * width + c, v);
+                if (ids && ids[t * top + j] >= experts) {
+                    load8(y + t * y_ld + c, v);
+                } else {
+                    const size_t row = place ? (size_t)place[t * top + j] : t * top + j;
+                    load8(expert_out + row * width + c, v);
+                }
 #pragma unroll
                 for (int i = 0; i < 8; ++i) acc[i] = fmaf(w, v[i], acc[i]);
             }
@@ -451,6 +463,10 @@ __global__ void moe_combine_kernel(const T* __restrict__ expert_out, const float
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
         float acc = 0.f;
         for (int j = 0; j < top; ++j) {
+            if (ids && ids[t * top + j] >= experts) {
+                acc = fmaf(weights[t * top + j], to_float(y[t * y_ld + c]), acc);
+                continue;
+            }
             const size_t row = place ? (size_t)place[t * top + j] : t * top + j;
             acc = fmaf(weights[t * top + j], to_float(expert_out[row * width + c]), acc);
         }
@@ -471,7 +487,8 @@ int fsie_moe_tile_rows() { return MOE_TILE; }
 // [experts] or null; ids int32 / weights float32 [tokens, top].
 int fsie_moe_route(const void* y, int y_ld, const float* w_router, const float* logits, const float* correction, int* ids,
                    float* weights, int tokens, int width, int experts, int top, int groups, int keep,
-                   float scale, int softmax_scores, int normalise, int dtype, cudaStream_t stream) {
+                   float scale, int softmax_scores, int normalise, int group_max, int dtype,
+                   cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if ((y && width <= 0) || experts <= 0 || top <= 0 || top > experts || groups <= 0 || experts % groups ||
         keep <= 0 || keep > groups || top > keep * (experts / groups))
@@ -486,13 +503,13 @@ int fsie_moe_route(const void* y, int y_ld, const float* w_router, const float* 
             cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return launch_dependent(moe_route_kernel<float>, tokens, threads, smem, stream, (const float*)y, y_ld, w_router,
                                 logits, correction, ids, weights, width, experts, top, groups, keep, scale,
-                                softmax_scores, normalise);
+                                softmax_scores, normalise, group_max);
     }
     if (smem > 48 * 1024)
         cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     return launch_dependent(moe_route_kernel<bf16>, tokens, threads, smem, stream, (const bf16*)y, y_ld, w_router,
                             logits, correction, ids, weights, width, experts, top, groups, keep, scale, softmax_scores,
-                            normalise);
+                            normalise, group_max);
 }
 
 // offsets [experts + 1], sorted [pairs] (padded: [(pairs / tile + experts) * tile]), tile_expert /
@@ -519,44 +536,49 @@ int fsie_moe_gather(const void* x, long long x_ld, const int* sorted, const int*
 }
 
 // gated = 1: x [tokens, x_ld] read at pair / top, w [experts, 2 n, k] (gate rows, then up rows), out
-// [pairs, out_ld] in sorted order.  gated = 0: x [pairs, x_ld] in sorted order, w [experts, n, k], out
+// [pairs, out_ld] in sorted order.  gated = 2: the same rows in and out, w [experts, n, k], out = f(x w^T)
+// (an expert without a gate: gate_kind names f).  gated = 0: x [pairs, x_ld] in sorted order, w [experts, n, k], out
 // written at the pair's own row.
 int fsie_moe_product(const void* x, long long x_ld, const void* w, void* out, long long out_ld,
                      const int* offsets, const int* sorted, const int* tile_expert, const int* tile_row0,
                      const int* meta, int pairs, int experts, int top, int n, int k, int gated, int gate_kind,
                      int dtype, cudaStream_t stream) {
     if (pairs <= 0 || n <= 0) return 0;
-    if (k <= 0 || experts <= 0 || top <= 0) return ERR_BAD_ARGUMENT;
-    const int cols = gated ? MOE_TILE / 2 : MOE_TILE;
+    if (k <= 0 || experts <= 0 || top <= 0 || gated < 0 || gated > 2) return ERR_BAD_ARGUMENT;
+    const int cols = gated == 1 ? MOE_TILE / 2 : MOE_TILE;
     const dim3 grid(pairs / MOE_TILE + experts, (n + cols - 1) / cols);
     if (grid.y > 65535) return ERR_UNSUPPORTED;
     if (dtype == DTYPE_BF16 && k % 8 == 0 && x_ld % 8 == 0 && ((((size_t)x) | ((size_t)w)) & 15) == 0) {
-        if (gated)
-            return launch_dependent(moe_product_mma_kernel<true>, grid, dim3(128), 0, stream, (const bf16*)x, x_ld,
-                                    (const bf16*)w, (bf16*)out, out_ld, offsets, sorted, tile_expert, tile_row0,
-                                    meta, top, n, k, gate_kind);
-        return launch_dependent(moe_product_mma_kernel<false>, grid, dim3(128), 0, stream, (const bf16*)x, x_ld,
-                                (const bf16*)w, (bf16*)out, out_ld, offsets, sorted, tile_expert, tile_row0, meta,
-                                top, n, k, gate_kind);
+#define FSIE_MOE_MMA(M)                                                                                      \
+        launch_dependent(moe_product_mma_kernel<M>, grid, dim3(128), 0, stream, (const bf16*)x, x_ld,              \
+                         (const bf16*)w, (bf16*)out, out_ld, offsets, sorted, tile_expert, tile_row0, meta, top, n, \
+                         k, gate_kind)
+        return gated == 1 ? FSIE_MOE_MMA(1) : (gated == 2 ? FSIE_MOE_MMA(2) : FSIE_MOE_MMA(0));
+#undef FSIE_MOE_MMA
     }
 #define FSIE_MOE(T, G)                                                                                      \
     launch_dependent(moe_product_kernel<T, G>, grid, dim3(256), 0, stream, (const T*)x, x_ld, (const T*)w, \
                      (T*)out, out_ld, offsets, sorted, tile_expert, tile_row0, meta, top, n, k, gate_kind)
-    if (dtype == DTYPE_F32) return gated ? FSIE_MOE(float, true) : FSIE_MOE(float, false);
-    return gated ? FSIE_MOE(bf16, true) : FSIE_MOE(bf16, false);
+    if (dtype == DTYPE_F32) return gated == 1 ? FSIE_MOE(float, 1) : (gated == 2 ? FSIE_MOE(float, 2) : FSIE_MOE(float, 0));
+    return gated == 1 ? FSIE_MOE(bf16, 1) : (gated == 2 ? FSIE_MOE(bf16, 2) : FSIE_MOE(bf16, 0));
 #undef FSIE_MOE
 }
 
+// ids [tokens, top] with `experts` and y [tokens, y_ld] (or all null): a choice at or beyond `experts` is an
+// identity expert, whose output is the token's row of y.
 // expert_out [tokens * top, width] at the pairs' rows (or, with `place`, pair p at row place[p]);
 // weights float32 [tokens, top]; shared [tokens, width] or null; out [tokens, width].
 int fsie_moe_combine(const void* expert_out, const float* weights, const void* shared, const int* place, void* out,
-                     int tokens, int width, int top, int dtype, cudaStream_t stream) {
+                     int tokens, int width, int top, const int* ids, int experts, const void* y, long long y_ld,
+                     int dtype, cudaStream_t stream) {
     if (tokens <= 0 || width <= 0) return 0;
-    const bool vec = width % 8 == 0 &&
-        (((size_t)expert_out | (size_t)shared | (size_t)out) & 15) == 0;
+    if (ids && !y) return ERR_BAD_ARGUMENT;
+    const bool vec = width % 8 == 0 && (!ids || y_ld % 8 == 0) &&
+        (((size_t)expert_out | (size_t)shared | (size_t)out | (size_t)y) & 15) == 0;
     const int threads = vec ? (width >= 2048 ? 256 : (width >= 1024 ? 128 : 64)) : (width >= 1024 ? 256 : 128);
 #define FSIE_COMBINE(T, V) launch_dependent(moe_combine_kernel<T, V>, tokens, threads, 0, stream, (const T*)expert_out, \
-                                            weights, (const T*)shared, place, (T*)out, width, top)
+                                            weights, (const T*)shared, place, (T*)out, width, top, ids, experts, \
+                                            (const T*)y, y_ld)
     if (dtype == DTYPE_F32) return vec ? FSIE_COMBINE(float, true) : FSIE_COMBINE(float, false);
     return vec ? FSIE_COMBINE(bf16, true) : FSIE_COMBINE(bf16, false);
 #undef FSIE_COMBINE

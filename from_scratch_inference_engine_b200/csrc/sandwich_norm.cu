@@ -194,6 +194,71 @@ static int norm_add_norm_launch(float* x, const void* delta, const float* gain_d
     return FSIE_LAUNCH_CHECK();
 }
 
+// x[s] += a1 * d1[s] + a2 * d2[s] (either may be null); y[r] = T( x[s] / sqrt(mean(x[s]^2) + eps) * gain ).
+// The outputs of two mixers that run side by side, each with its weight, meet the 32-bit residual
+// stream here without being summed in the storage type first.  VEC: width a multiple of 8, rows on
+// 16 bytes, eight columns per thread and trip.
+template <typename T, bool VEC>
+__global__ void scaled_sum_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ d1, float a1,
+                                          const T* __restrict__ d2, float a2, const float* __restrict__ gain,
+                                          T* __restrict__ y, const int* __restrict__ rows, int hidden,
+                                          float eps, int write_x) {
+    extern __shared__ __align__(16) float ssr_row[];
+    __shared__ float scratch[32];
+    grid_dependency_wait();
+    grid_dependents_go();
+    const int r = blockIdx.x;
+    const size_t s = rows ? (size_t)rows[r] : (size_t)r;
+    float* xr = x + s * hidden;
+    const T* p1 = d1 ? d1 + s * hidden : nullptr;
+    const T* p2 = d2 ? d2 + s * hidden : nullptr;
+    constexpr int STEP = VEC ? 8 : 1;
+    float ss = 0.f;
+    for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], d[8];
+            load8(xr + c, v);
+            if (p1) {
+                load8(p1 + c, d);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = fmaf(a1, d[e], v[e]);
+            }
+            if (p2) {
+                load8(p2 + c, d);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = fmaf(a2, d[e], v[e]);
+            }
+            if (write_x) store8(xr + c, v);
+            store8(ssr_row + c, v);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+        } else {
+            float v = xr[c];
+            if (p1) v = fmaf(a1, to_float(p1[c]), v);
+            if (p2) v = fmaf(a2, to_float(p2[c]), v);
+            if (write_x) xr[c] = v;
+            ssr_row[c] = v;
+            ss += v * v;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    if (!y) return;
+    const float scale = 1.0f / sqrtf(ss / (float)hidden + eps);
+    T* yr = y + (size_t)r * hidden;
+    for (int c = threadIdx.x * STEP; c < hidden; c += blockDim.x * STEP) {
+        if (VEC) {
+            float v[8], g[8];
+            load8(ssr_row + c, v);
+            load8(gain + c, g);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = (v[e] * scale) * g[e];
+            store8(yr + c, v);
+        } else {
+            yr[c] = from_float<T>((ssr_row[c] * scale) * gain[c]);
+        }
+    }
+}
+
 }  // namespace fsie
 
 using namespace fsie;
@@ -237,6 +302,31 @@ int fsie_gated_act(const void* gu, void* act, long long tokens, int inter, int k
                                 (const float*)gu, (float*)act, inter, total, kind);
     return launch_dependent(gated_act_kernel<bf16>, dim3(blocks), dim3(threads), 0, stream,
                             (const bf16*)gu, (bf16*)act, inter, total, kind);
+}
+
+// x float32 [*, hidden]; d1, d2 and y of storage type `dtype` (any may be null); gain float32 [hidden].
+int fsie_scaled_sum_rmsnorm(float* x, const void* d1, float a1, const void* d2, float a2, const float* gain,
+                            void* y, const int* rows, int num_rows, int hidden, float eps, int write_x,
+                            int dtype, cudaStream_t stream) {
+    if (num_rows <= 0) return 0;
+    if (hidden <= 0 || (y && !gain)) return ERR_BAD_ARGUMENT;
+    const size_t smem = (size_t)hidden * sizeof(float);
+    if (smem > 200 * 1024) return ERR_UNSUPPORTED;
+    const bool vec = hidden % 8 == 0 &&
+        ((((size_t)x) | ((size_t)d1) | ((size_t)d2) | ((size_t)y) | ((size_t)gain)) & 15) == 0;
+    const int threads = vec ? (hidden >= 4096 ? 512 : (hidden >= 1024 ? 128 : 64))
+                            : (hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128));
+#define FSIE_SSR(T, V)                                                                                      \
+    do {                                                                                                    \
+        if (smem > 48 * 1024)                                                                               \
+            cudaFuncSetAttribute(scaled_sum_rmsnorm_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)smem);                                                                \
+        return launch_dependent(scaled_sum_rmsnorm_kernel<T, V>, dim3(num_rows), dim3(threads), smem, stream, x, \
+                                (const T*)d1, a1, (const T*)d2, a2, gain, (T*)y, rows, hidden, eps, write_x); \
+    } while (0)
+    if (dtype == DTYPE_F32) { if (vec) FSIE_SSR(float, true); else FSIE_SSR(float, false); }
+    if (vec) FSIE_SSR(bf16, true); else FSIE_SSR(bf16, false);
+#undef FSIE_SSR
 }
 
 }  // extern "C"

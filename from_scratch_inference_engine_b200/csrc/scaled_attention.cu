@@ -5,6 +5,7 @@
 // and the output.
 //
 //   s_h(i, j) = (q_h,i . k_g(h),j) * head_scale[h]      visible: j <= i and (window == 0 or i - j < window)
+//                                                       and (chunk == 0 or i / chunk == j / chunk)
 //   o_h,i     = sum_j softmax_j(s_h(i, .)) v_g(h),j      g(h) = h / (heads / kv_heads)
 //
 // Work is cut as in attention_generic.cu: a tile is up to ROWS query rows of one request and one
@@ -36,8 +37,16 @@ struct ScaledAttnParams {
     void* out; int out_ld;                    // head h of token t at t * out_ld + h * value_dim
     float* part_o; float* part_ml;            // [nsplit, tokens, heads, value_dim], [nsplit, tokens, heads, 2]
     int tokens, heads, kv_heads, window, nsplit;
+    int chunk;                                // > 0: a query sees only the keys of its own chunk of this many positions
     int* error;
 };
+
+// The first key that the query at `pos` sees: the window's start, or the start of its chunk.
+__device__ __forceinline__ int sa_first_key(const ScaledAttnParams& p, int pos) {
+    int first = p.window > 0 ? pos - p.window + 1 : 0;
+    if (p.chunk > 0) first = max(first, pos - pos % p.chunk);
+    return max(first, 0);
+}
 
 template <typename T, int DPL, bool SHARED_V>
 __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const ScaledAttnParams p) {
@@ -77,7 +86,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
 
     const int pos_first = pos0 + row0 / group;
     const int pos_last = pos0 + (row0 + nrows - 1) / group;
-    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kbegin = sa_first_key(p, pos_first);
     int kend = pos_last + 1;
     if (p.nsplit > 1) {
         const int span = kend - kbegin;
@@ -89,12 +98,13 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
     }
 
     float m[SA_RPW], l[SA_RPW], acc[SA_RPW][DPL];
-    int pos[SA_RPW];
+    int pos[SA_RPW], first_key[SA_RPW];
 #pragma unroll
     for (int i = 0; i < SA_RPW; ++i) {
         m[i] = -INFINITY; l[i] = 0.f;
         const int r = warp * SA_RPW + i;
         pos[i] = r < nrows ? pos0 + (row0 + r) / group : -1;       // -1: no row, sees nothing
+        first_key[i] = sa_first_key(p, pos[i]);
 #pragma unroll
         for (int c = 0; c < DPL; ++c) acc[i][c] = 0.f;
     }
@@ -110,7 +120,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
                     const long long at = (long long)kvh * p.page_size + kj % p.page_size;
                     kb = (long long)page * p.page_stride + at * dk;
                     vb = (long long)page * p.page_stride + at * p.value_ld;
-                } else if (kj <= pos_last && (p.window <= 0 || kj > pos_first - p.window) && p.error) {
+                } else if (kj <= pos_last && kj >= sa_first_key(p, pos_first) && p.error) {
                     atomicExch(p.error, 3);            // some row of the tile sees this key, and its page was given back
                 }
             }
@@ -151,7 +161,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_kernel(const S
         bool any = false;
 #pragma unroll
         for (int i = 0; i < SA_RPW; ++i) {
-            const bool seen = key_ok && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+            const bool seen = key_ok && kj <= pos[i] && kj >= first_key[i];
             const float si = seen ? s[i] : -INFINITY;
             const float m_new = fmaxf(m[i], warp_max(si));
             if (m_new == -INFINITY) { pj[i] = 0.f; continue; }       // uniform over the warp
@@ -291,7 +301,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
 
     const int pos_first = pos0 + row0 / group;
     const int pos_last = pos0 + (row0 + nrows - 1) / group;
-    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kbegin = sa_first_key(p, pos_first);
     int kend = pos_last + 1;
     if (p.nsplit > 1) {
         const int span = kend - kbegin;
@@ -314,7 +324,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
         const int j = tid / TPR, part = tid % TPR;
         const int kj = k0 + j;
         if (kj < kend && page < 0 && part == 0 && p.error && kj <= pos_last &&
-            (p.window <= 0 || kj > pos_first - p.window))
+            kj >= sa_first_key(p, pos_first))
             atomicExch(p.error, 3);                // some row of the tile sees this key, and its page was given back
         const bool ok = page >= 0;
         const long long at = (long long)kvh * p.page_size + kj % p.page_size;
@@ -344,12 +354,13 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
     }
 
     // this thread's two rows: g and g + 8 of its group of 16
-    int pos[2];
+    int pos[2], first_key[2];
     float sc[2], m[2], l[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = mi * 16 + g + 8 * i;
         pos[i] = r < nrows ? pos0 + (row0 + r) / group : -1;
+        first_key[i] = sa_first_key(p, pos[i]);
         sc[i] = r < nrows ? p.head_scale[kvh * group + (row0 + r) % group] : 0.f;
         m[i] = -INFINITY; l[i] = 0.f;
     }
@@ -392,7 +403,7 @@ __global__ void __launch_bounds__(SA_WARPS * 32) scaled_attention_mma_kernel(con
                 const int i = e >> 1;
                 const int j = vi * 16 + n * 8 + 2 * t + (e & 1);
                 const int kj = k0 + j;
-                seen[n][e] = kj < kend && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+                seen[n][e] = kj < kend && kj <= pos[i] && kj >= first_key[i];
                 s[n][e] = seen[n][e] ? s[n][e] * sc[i] : -INFINITY;
                 tmax[i] = fmaxf(tmax[i], s[n][e]);
             }
@@ -544,7 +555,7 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
 
     const int pos_first = pos0 + row0 / group;
     const int pos_last = pos0 + (row0 + nrows - 1) / group;
-    int kbegin = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int kbegin = sa_first_key(p, pos_first);
     int kend = pos_last + 1;
     if (p.nsplit > 1) {
         const int span = kend - kbegin;
@@ -567,7 +578,7 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
         const int j = tid / TPR, part = tid % TPR;
         const int kj = k0 + j;
         if (kj < kend && page < 0 && part == 0 && p.error && kj <= pos_last &&
-            (p.window <= 0 || kj > pos_first - p.window))
+            kj >= sa_first_key(p, pos_first))
             atomicExch(p.error, 3);                // some row of the tile sees this key, and its page was given back
         const bool ok = page >= 0;
         const long long at = (long long)kvh * p.page_size + kj % p.page_size;
@@ -595,12 +606,13 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
         }
     }
 
-    int pos[2];
+    int pos[2], first_key[2];
     float sc[2], m[2], l[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
         const int r = warp * 16 + g + 8 * i;
         pos[i] = r < nrows ? pos0 + (row0 + r) / group : -1;
+        first_key[i] = sa_first_key(p, pos[i]);
         sc[i] = r < nrows ? p.head_scale[kvh * group + (row0 + r) % group] : 0.f;
         m[i] = -INFINITY; l[i] = 0.f;
     }
@@ -622,7 +634,7 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
             issue_tile(stage ^ 1, k0 + TM_KT, page_ahead);
             page_ahead = page_of(k0 + 2 * TM_KT);
         }
-        if (k0 > warp_last || (p.window > 0 && k0 + TM_KT - 1 <= warp_first - p.window)) continue;
+        if (k0 > warp_last || k0 + TM_KT - 1 < sa_first_key(p, warp_first)) continue;
         // ---- scores of 16 rows x 64 keys
         float s[8][4];
 #pragma unroll
@@ -650,7 +662,7 @@ __global__ void __launch_bounds__(TR_WARPS * 32) scaled_attention_rows_kernel(co
                 const int i = e >> 1;
                 const int j = n * 8 + 2 * t + (e & 1);
                 const int kj = k0 + j;
-                const bool seen = kj < kend && kj <= pos[i] && (p.window <= 0 || kj > pos[i] - p.window);
+                const bool seen = kj < kend && kj <= pos[i] && kj >= first_key[i];
                 s[n][e] = seen ? s[n][e] * sc[i] : -INFINITY;
                 tmax[i] = fmaxf(tmax[i], s[n][e]);
             }
@@ -818,6 +830,89 @@ __global__ void rotate_mix_write_kernel(T* __restrict__ proj, int ld, const int*
     }
 }
 
+// One block per token of proj = [ q (heads x dim) | k (kv_heads x dim) | v (kv_heads x vdim) | ... ],
+// a warp per head of q and k in turn.
+//   q, k   with gains (q_gain, k_gain [dim], shared by the heads): every head divided by its root
+//          mean square (eps inside the root) times the gain, in 32-bit, BEFORE the rotation;
+//          then pairs (i, i + rotary_dim / 2) turn by the token's angles; q in place, k into its page
+//   v      into its page as it is
+template <typename T>
+__global__ void norm_rotate_write_kernel(T* __restrict__ proj, int ld, const int* __restrict__ positions,
+                                         const float* __restrict__ cos_sin, int table_len,
+                                         const int* __restrict__ slot_of, T* __restrict__ k_pages,
+                                         T* __restrict__ v_pages, long long page_stride, int page_size,
+                                         int heads, int kv_heads, int dim, int vdim, int rotary_dim,
+                                         const float* __restrict__ q_gain, const float* __restrict__ k_gain,
+                                         float eps, int* __restrict__ error) {
+    extern __shared__ float nr_smem[];                 // [warps][dim]
+    const int t = blockIdx.x;
+    grid_dependency_wait();
+    grid_dependents_go();
+    const int pos = positions[t];
+    if (rotary_dim > 0 && (pos < 0 || pos >= table_len)) {
+        if (threadIdx.x == 0) atomicExch(error, 2);
+        return;
+    }
+    const int half = rotary_dim / 2;
+    const float* cs = cos_sin + (size_t)pos * rotary_dim;
+    T* row = proj + (size_t)t * ld;
+    const int slot = slot_of ? slot_of[t] : -1;
+    const long long page = slot >= 0 ? slot / page_size : -1;
+    const int off = slot >= 0 ? slot % page_size : 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float* mine = nr_smem + (size_t)warp * dim;
+    for (int h = warp; h < heads + kv_heads; h += warps) {
+        const bool is_q = h < heads;
+        if (!is_q && slot < 0) continue;               // nothing to store (uniform over the warp)
+        T* src = row + (size_t)h * dim;
+        const float* gain = is_q ? q_gain : k_gain;
+        float sq = 0.f;
+        for (int d = lane; d < dim; d += 32) {
+            const float v = to_float(src[d]);
+            mine[d] = v;
+            sq += v * v;
+        }
+        if (gain) {
+            const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)dim + eps);
+            for (int d = lane; d < dim; d += 32) mine[d] = mine[d] * inv * gain[d];
+        }
+        __syncwarp();
+        T* dst = is_q ? src : k_pages + page * page_stride + ((long long)(h - heads) * page_size + off) * dim;
+        for (int d = lane; d < dim; d += 32) {
+            float val = mine[d];
+            if (d < rotary_dim) {
+                const int i = d < half ? d : d - half;
+                const float c = cs[i], sn = cs[half + i];
+                const float other = mine[d < half ? d + half : d - half];
+                val = d < half ? val * c - other * sn : val * c + other * sn;
+            }
+            dst[d] = from_float<T>(val);
+        }
+        __syncwarp();
+    }
+    if (slot < 0) return;
+    const T* v = row + (size_t)(heads + kv_heads) * dim;
+    for (int e = threadIdx.x; e < kv_heads * vdim; e += blockDim.x) {
+        const int g = e / vdim, d = e - g * vdim;
+        v_pages[page * page_stride + ((long long)g * page_size + off) * vdim + d] = v[e];
+    }
+}
+
+// out[t, h, :] <- out[t, h, :] * sigmoid(gate[t, h]): one number per token and head.
+template <typename T>
+__global__ void head_gate_kernel(T* __restrict__ out, int out_ld, const T* __restrict__ gate, int gate_ld,
+                                 int heads, int vdim) {
+    grid_dependency_wait();
+    grid_dependents_go();
+    const size_t t = blockIdx.x;
+    T* o = out + t * out_ld;
+    const T* g = gate + t * gate_ld;
+    for (int c = threadIdx.x; c < heads * vdim; c += blockDim.x) {
+        const float s = 1.0f / (1.0f + expf(-to_float(g[c / vdim])));
+        o[c] = from_float<T>(to_float(o[c]) * s);
+    }
+}
+
 template <typename T, int DPL>
 static int scaled_attention_launch(const ScaledAttnParams& p, int tiles, bool shared_v, cudaStream_t stream) {
     const int dk4 = (p.key_dim + 3) & ~3;
@@ -912,11 +1007,12 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
                           const int* tile_item, const int* tile_row0, int tiles, const int* item_qstart,
                           const int* item_qlen, const int* item_pos0, const int* item_slots, void* out,
                           int out_ld, float* part_o, float* part_ml, int tokens, int heads, int kv_heads,
-                          int window, int nsplit, int dtype, int form, int* error, cudaStream_t stream) {
+                          int window, int chunk, int nsplit, int dtype, int form, int* error,
+                          cudaStream_t stream) {
     if (tokens <= 0 || tiles <= 0) return 0;
     if (tiles > 65535 || nsplit > 65535) return ERR_UNSUPPORTED;
     if (key_dim <= 0 || value_dim <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || nsplit < 1 ||
-        page_size <= 0 || window < 0 || (values_in_keys && value_dim > key_dim))
+        page_size <= 0 || window < 0 || chunk < 0 || (values_in_keys && value_dim > key_dim))
         return ERR_BAD_ARGUMENT;
     if (nsplit > 1 && (!part_o || !part_ml)) return ERR_BAD_ARGUMENT;
     ScaledAttnParams p;
@@ -929,6 +1025,7 @@ int fsie_scaled_attention(const void* q, int q_ld, const float* head_scale, cons
     p.item_qstart = item_qstart; p.item_qlen = item_qlen; p.item_pos0 = item_pos0; p.item_slots = item_slots;
     p.out = out; p.out_ld = out_ld; p.part_o = part_o; p.part_ml = part_ml;
     p.tokens = tokens; p.heads = heads; p.kv_heads = kv_heads; p.window = window; p.nsplit = nsplit;
+    p.chunk = chunk;
     p.error = error;
     int rc;
     const int tile_rows = fsie_scaled_attention_tile_rows(dtype, key_dim, value_dim, values_in_keys, form);
@@ -987,6 +1084,45 @@ int fsie_rotate_mix_write(void* proj, int ld, const int* positions, const float*
                             (bf16*)proj, ld, positions, cos_sin, table_len, slot_of, (bf16*)k_pages,
                             (bf16*)v_pages, page_stride, page_size, heads, kv_heads, dim, vdim,
                             rotary_dim, mix_mode, mix, (bf16*)v_first, error);
+}
+
+
+// proj [tokens, ld] = q | k | v head by head (more columns may follow); q_gain / k_gain [dim] float or
+// null (no norm of that side); cos_sin [table_len, rotary_dim]; slot_of [tokens] (page * page_size +
+// offset, -1: store nothing).
+int fsie_norm_rotate_write(void* proj, int ld, const int* positions, const float* cos_sin, int table_len,
+                           const int* slot_of, void* k_pages, void* v_pages, long long page_stride,
+                           int page_size, int tokens, int heads, int kv_heads, int dim, int vdim,
+                           int rotary_dim, const float* q_gain, const float* k_gain, float eps, int dtype,
+                           int* error, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (rotary_dim < 0 || rotary_dim > dim || (rotary_dim & 1) || dim <= 0 ||
+        ld < (heads + kv_heads) * dim + kv_heads * vdim)
+        return ERR_BAD_ARGUMENT;
+    const int warps = 8;
+    const size_t smem = (size_t)warps * dim * sizeof(float);
+    if (smem > 48 * 1024) return ERR_UNSUPPORTED;
+    if (dtype == DTYPE_F32)
+        return launch_dependent(norm_rotate_write_kernel<float>, dim3(tokens), dim3(warps * 32), smem, stream,
+                                (float*)proj, ld, positions, cos_sin, table_len, slot_of, (float*)k_pages,
+                                (float*)v_pages, page_stride, page_size, heads, kv_heads, dim, vdim, rotary_dim,
+                                q_gain, k_gain, eps, error);
+    return launch_dependent(norm_rotate_write_kernel<bf16>, dim3(tokens), dim3(warps * 32), smem, stream,
+                            (bf16*)proj, ld, positions, cos_sin, table_len, slot_of, (bf16*)k_pages,
+                            (bf16*)v_pages, page_stride, page_size, heads, kv_heads, dim, vdim, rotary_dim,
+                            q_gain, k_gain, eps, error);
+}
+
+// out [tokens, out_ld] holds heads x vdim columns per token, gate [tokens, gate_ld] one column per head.
+int fsie_head_gate(void* out, int out_ld, const void* gate, int gate_ld, int tokens, int heads, int vdim,
+                   int dtype, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0 || vdim <= 0) return 0;
+    const int threads = heads * vdim >= 1024 ? 256 : 128;
+    if (dtype == DTYPE_F32)
+        return launch_dependent(head_gate_kernel<float>, dim3(tokens), dim3(threads), 0, stream, (float*)out,
+                                out_ld, (const float*)gate, gate_ld, heads, vdim);
+    return launch_dependent(head_gate_kernel<bf16>, dim3(tokens), dim3(threads), 0, stream, (bf16*)out, out_ld,
+                            (const bf16*)gate, gate_ld, heads, vdim);
 }
 
 }  // extern "C"

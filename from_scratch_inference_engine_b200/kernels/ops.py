@@ -16,7 +16,8 @@ import torch
 from ..csrc import build
 
 DTYPE_F32, DTYPE_BF16 = 0, 1
-GATE_KINDS = {"silu": 0, "gelu_tanh": 1}       # activations a gated feed-forward may put on its gate
+GATE_KINDS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}   # activations of a feed-forward ("relu2": the square of relu)
+FUSED_GATES = ("silu", "gelu_tanh")        # ... those that the matrix products' gated epilogues know
 
 
 class KernelError(RuntimeError):
@@ -743,9 +744,16 @@ class GroupedTiledWeight:
     descriptor over all of them.  For SwiGLU each matrix holds the gate rows and then as many up
     rows."""
 
-    def __init__(self, weight: torch.Tensor, swiglu: bool = False, activation: str = "silu"):
+    def __init__(self, weight: torch.Tensor, swiglu: bool = False, activation: str = "silu",
+                 plain_activation: Optional[str] = None):
         _need(weight, torch.bfloat16, "weight")
+        if swiglu and GATE_KINDS[activation] > 1:
+            raise KernelError("gemm_tiles_grouped: the gate is SiLU or the tanh form of GELU")
         self.gate = 1 + GATE_KINDS[activation] if swiglu else 0
+        if plain_activation is not None:       # no gate: the activation on the product itself
+            if swiglu or plain_activation != "relu2":
+                raise KernelError("gemm_tiles_grouped: without a gate the activation is 'relu2'")
+            self.gate = 3
         groups, rows, k = weight.shape
         if k % 8 or (swiglu and rows % 2):
             raise KernelError("gemm_tiles_grouped: K must be a multiple of 8, a SwiGLU matrix hold "
@@ -834,19 +842,42 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 _hybrid = None
 
 
+_scan = None
+
+
+def scan():
+    """The library of recurrences over per-request state of the form S <- a S + k v^T, o = S^T q
+    (decaying linear attention; a state-space mixer with its convolution, step sizes and gated
+    norm), compiled at first use."""
+    global _scan
+    if _scan is None:
+        lib = build.load_library("scan")
+        i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
+        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, p, p, i, i, p,
+                                            i, p, ll, p]
+        lib.fsie_silu_rows.argtypes = [p, i, i, p, i, i, p]
+        lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
+        lib.fsie_ssd_max_taps.argtypes = []
+        lib.fsie_ssd_prep.argtypes = [p, i, i, i, p, p, p, i, p, ll, ll, p, p, i, i, p, p, i, i, p, i, p,
+                                      i, i, p]
+        lib.fsie_ssd_tails.argtypes = [p, i, i, p, p, p, i, p, ll, ll, i, i, i, p]
+        lib.fsie_ssd_gate_norm.argtypes = [p, p, i, p, i, i, p, p, p, i, i, i, i, f, i, p]
+        for name in ("fsie_lightning_scan", "fsie_silu_rows", "fsie_gated_rmsnorm", "fsie_ssd_max_taps",
+                     "fsie_ssd_prep", "fsie_ssd_tails", "fsie_ssd_gate_norm"):
+            getattr(lib, name).restype = i
+        _scan = lib
+    return _scan
+
+
 def hybrid():
-    """The library of the hybrid decoders' parts (layer norm on a sublayer's output, decaying
-    linear attention, windowed attention with mixed heads), compiled at first use."""
+    """The library of the hybrid decoders' parts (layer norm on a sublayer's output, windowed
+    attention with mixed heads), compiled at first use."""
     global _hybrid
     if _hybrid is None:
         lib = build.load_library("hybrid")
         i, f, ll, p = ctypes.c_int, ctypes.c_float, ctypes.c_longlong, ctypes.c_void_p
         lib.fsie_add_layernorm.argtypes = [p, p, p, p, p, i, i, f, i, i, p]
         lib.fsie_cast_rows.argtypes = [p, p, ll, i, p]
-        lib.fsie_lightning_scan.argtypes = [p, i, i, i, i, p, p, p, i, p, p, p, i, i, i, p, p, i, i, p, p]
-        lib.fsie_silu_rows.argtypes = [p, i, i, p, i, i, p]
-        lib.fsie_silu_rows.restype = i
-        lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
         lib.fsie_conv_norm_rotate.argtypes = [p, i, i, i, p, p, p, p, p, i, p, p, p, i, i, p, p, p,
                                               ll, i, p, i, i, i, i, i, f, i, p, p]
         lib.fsie_conv_tails.argtypes = [p, i, p, p, p, i, p, i, i, i, p]
@@ -859,8 +890,7 @@ def hybrid():
                                                    i, i, i, i, i, i, i, f, p, p]
         lib.fsie_talking_attention_mma_takes.restype = i
         lib.fsie_talking_attention_mma.restype = i
-        for name in ("fsie_add_layernorm", "fsie_cast_rows", "fsie_lightning_scan",
-                     "fsie_gated_rmsnorm", "fsie_conv_norm_rotate", "fsie_conv_tails",
+        for name in ("fsie_add_layernorm", "fsie_cast_rows", "fsie_conv_norm_rotate", "fsie_conv_tails",
                      "fsie_talking_attention_tile_tokens", "fsie_talking_attention_key_tile",
                      "fsie_talking_attention"):
             getattr(lib, name).restype = i
@@ -929,7 +959,7 @@ def silu_rows(proj: torch.Tensor, width: int, act: torch.Tensor) -> torch.Tensor
     tokens, ld = proj.shape
     if width > ld or act.numel() < tokens * width:
         raise KernelError("silu_rows: shapes do not fit")
-    _check(hybrid().fsie_silu_rows(_ptr(proj), ld, width, _ptr(act), tokens, _tag(proj.dtype),
+    _check(scan().fsie_silu_rows(_ptr(proj), ld, width, _ptr(act), tokens, _tag(proj.dtype),
                                    _stream()), "silu_rows")
     return act
 
@@ -939,11 +969,15 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                    items: int, state: torch.Tensor, decay: torch.Tensor, out: torch.Tensor,
                    heads: int, dim: int, vdim: int, seg_item: Optional[torch.Tensor] = None,
                    seg_row0: Optional[torch.Tensor] = None, num_segs: int = 0, seg_tokens: int = 0,
-                   chunk_states: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   chunk_states: Optional[torch.Tensor] = None, share: int = 1,
+                   decay_tok: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Per request and head, token by token: S = decay * S + k v^T, o = S^T q.  proj [tokens, ld]
     (float32) holds the ACTIVATED projections (`silu_rows`) at the given column offsets; state
-    [slots, heads, dim, vdim] (float32) is read and left updated; out [tokens, heads * vdim]
-    float32.
+    [slots, heads, dim, vdim] (float32; or [slots, n] with the heads' matrices in the first
+    heads * dim * vdim floats of a slot) is read and left updated; out [tokens, heads * vdim]
+    float32.  `decay_tok` (float32 [tokens, heads]) gives a decay per token and head in place of
+    `decay`; `share` heads in a row read the same q and k columns (q and k then hold heads / share
+    column groups of `dim`).
 
     With `seg_item` / `seg_row0` (int32, one entry per chunk of `seg_tokens` tokens, listed
     request by request) and `chunk_states` (float32, num_segs * heads * dim * vdim at least) the
@@ -951,14 +985,24 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
     the state at every chunk's start, and each chunk runs again from there for its outputs."""
     _need(proj, torch.float32, "proj")
     _need(state, torch.float32, "state")
-    _need(decay, torch.float32, "decay")
+    if decay is not None:
+        _need(decay, torch.float32, "decay")
     _need(out, torch.float32, "out")
     for name, t in (("item_qstart", item_qstart), ("item_qlen", item_qlen), ("item_slots", item_slots)):
         _need(t, torch.int32, name)
     tokens, ld = proj.shape
-    if max(q_off, k_off) + heads * dim > ld or v_off + heads * vdim > ld:
+    if share <= 0 or heads % share:
+        raise KernelError("lightning_scan: heads must be a multiple of share")
+    if max(q_off, k_off) + heads // share * dim > ld or v_off + heads * vdim > ld:
         raise KernelError("lightning_scan: projection rows are narrower than q, k and v")
-    if tuple(state.shape[1:]) != (heads, dim, vdim) or decay.numel() != heads:
+    if decay_tok is not None:
+        _need(decay_tok, torch.float32, "decay_tok")
+        if decay_tok.numel() < tokens * heads:
+            raise KernelError("lightning_scan: decay_tok is too small")
+    elif decay is None:
+        raise KernelError("lightning_scan: a decay per head or per token and head is needed")
+    state_stride = state.stride(0)
+    if state_stride < heads * dim * vdim or (decay is not None and decay.numel() != heads):
         raise KernelError("lightning_scan: state or decay does not fit the heads")
     if out.numel() < tokens * heads * vdim:
         raise KernelError("lightning_scan: out is too small")
@@ -968,11 +1012,88 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
         _need(chunk_states, torch.float32, "chunk_states")
         if chunk_states.numel() < num_segs * heads * dim * vdim:
             raise KernelError("lightning_scan: chunk_states is too small")
-    _check(hybrid().fsie_lightning_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(item_qstart),
-                                        _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),
-                                        _ptr(decay), _ptr(out), heads, dim, vdim, _ptr(seg_item),
-                                        _ptr(seg_row0), num_segs, seg_tokens, _ptr(chunk_states),
-                                        _stream()), "lightning_scan")
+    _check(scan().fsie_lightning_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(item_qstart),
+                                      _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),
+                                      _ptr(decay), _ptr(out), heads, dim, vdim, _ptr(seg_item),
+                                      _ptr(seg_row0), num_segs, seg_tokens, _ptr(chunk_states),
+                                      int(share), _ptr(decay_tok), state_stride, _stream()),
+           "lightning_scan")
+    return out
+
+
+def ssd_max_taps() -> int:
+    return int(scan().fsie_ssd_max_taps())
+
+
+def ssd_prep(proj: torch.Tensor, conv_off: int, dt_off: int, item_qstart: torch.Tensor,
+             item_qlen: torch.Tensor, item_slots: torch.Tensor, items: int,
+             state: Optional[torch.Tensor], tail_off: int, conv_w: torch.Tensor,
+             conv_b: Optional[torch.Tensor], dt_bias: torch.Tensor, a_log: torch.Tensor, heads: int,
+             vdim: int, act: torch.Tensor, decay: torch.Tensor) -> None:
+    """What a state-space mixer's scan reads, per token of proj [tokens, ld] (the stored projection
+    with the convolution's input columns at conv_off and the step sizes at dt_off):
+    act [tokens, channels + heads * vdim] float32 = [silu(causal convolution + bias) | dt * x] with x
+    the first heads * vdim convolved columns, dt = softplus(dt + dt_bias), and decay [tokens, heads]
+    = exp(-exp(a_log) * dt).  conv_w float32 [channels, taps], the last column the current token's;
+    the inputs of the taps - 1 tokens before a step's first live in the request's slot of `state`
+    [slots, n] (float32) from float tail_off on, oldest first (`ssd_tails` moves them on)."""
+    _need(proj, None, "proj")
+    _need(conv_w, torch.float32, "conv_w")
+    _need(dt_bias, torch.float32, "dt_bias")
+    _need(a_log, torch.float32, "a_log")
+    _need(act, torch.float32, "act")
+    _need(decay, torch.float32, "decay")
+    tokens, ld = proj.shape
+    channels, taps = conv_w.shape
+    if conv_off + channels > ld or dt_off + heads > ld or act.shape[1] < channels + heads * vdim or \
+            act.shape[0] < tokens or decay.numel() < tokens * heads or dt_bias.numel() != heads or \
+            a_log.numel() != heads or (conv_b is not None and conv_b.numel() != channels):
+        raise KernelError("ssd_prep: shapes do not fit")
+    stride = 0
+    if taps > 1:
+        _need(state, torch.float32, "state", contiguous=False)
+        stride = state.stride(0)
+        if tail_off + (taps - 1) * channels > stride:
+            raise KernelError("ssd_prep: the state slots do not hold the convolution's inputs")
+    _check(scan().fsie_ssd_prep(_ptr(proj), ld, conv_off, dt_off, _ptr(item_qstart), _ptr(item_qlen),
+                                _ptr(item_slots), items, _ptr(state), stride, tail_off, _ptr(conv_w),
+                                _ptr(conv_b), taps, channels, _ptr(dt_bias), _ptr(a_log), heads, vdim,
+                                _ptr(act), act.stride(0), _ptr(decay), tokens, _tag(proj.dtype),
+                                _stream()), "ssd_prep")
+
+
+def ssd_tails(proj: torch.Tensor, conv_off: int, channels: int, taps: int, item_qstart: torch.Tensor,
+              item_qlen: torch.Tensor, item_slots: torch.Tensor, items: int, state: torch.Tensor,
+              tail_off: int) -> None:
+    """After `ssd_prep`: every request's slot receives the convolution inputs of the last taps - 1
+    tokens of (what it held, then the step's tokens)."""
+    if taps <= 1:
+        return
+    _need(proj, None, "proj")
+    _need(state, torch.float32, "state", contiguous=False)
+    _check(scan().fsie_ssd_tails(_ptr(proj), proj.shape[1], conv_off, _ptr(item_qstart), _ptr(item_qlen),
+                                 _ptr(item_slots), items, _ptr(state), state.stride(0), tail_off, taps,
+                                 channels, _tag(proj.dtype), _stream()), "ssd_tails")
+
+
+def ssd_gate_norm(o: torch.Tensor, act: torch.Tensor, proj: torch.Tensor, z_off: int, skip: torch.Tensor,
+                  gain: torch.Tensor, out: torch.Tensor, vdim: int, parts: int, eps: float) -> torch.Tensor:
+    """out[t] = v / sqrt(mean over each of `parts` equal parts of v^2 + eps) * gain with
+    v = (o[t] + skip[head] * x[t]) * silu(z[t]); o float32 [tokens, inner], x the first inner
+    columns of act (float32), z = proj[t, z_off : z_off + inner] of the storage type."""
+    _need(o, torch.float32, "o")
+    _need(act, torch.float32, "act")
+    _need(proj, None, "proj")
+    _need(skip, torch.float32, "skip")
+    _need(gain, torch.float32, "gain")
+    _need(out, proj.dtype, "out")
+    tokens, inner = o.shape
+    if z_off + inner > proj.shape[1] or gain.numel() != inner or skip.numel() * vdim != inner or \
+            out.numel() < tokens * inner or act.shape[1] < inner:
+        raise KernelError("ssd_gate_norm: shapes do not fit")
+    _check(scan().fsie_ssd_gate_norm(_ptr(o), _ptr(act), act.stride(0), _ptr(proj), proj.shape[1], z_off,
+                                     _ptr(skip), _ptr(gain), _ptr(out), tokens, inner, vdim, int(parts),
+                                     float(eps), _tag(proj.dtype), _stream()), "ssd_gate_norm")
     return out
 
 
@@ -986,7 +1107,7 @@ def gated_rmsnorm(o: torch.Tensor, proj: torch.Tensor, g_off: int, gain: torch.T
     tokens, width = o.shape
     if g_off + width > proj.shape[1] or gain.numel() != width or out.numel() < tokens * width:
         raise KernelError("gated_rmsnorm: shapes do not fit")
-    _check(hybrid().fsie_gated_rmsnorm(_ptr(o), _ptr(proj), proj.shape[1], g_off, _ptr(gain),
+    _check(scan().fsie_gated_rmsnorm(_ptr(o), _ptr(proj), proj.shape[1], g_off, _ptr(gain),
                                        _ptr(out), tokens, width, float(eps), _tag(proj.dtype),
                                        _stream()), "gated_rmsnorm")
     return out
@@ -1171,14 +1292,19 @@ def mixers():
         lib.fsie_scaled_attention_tile_rows.argtypes = [i, i, i, i, i]
         lib.fsie_scaled_attention_tile_rows.restype = i
         lib.fsie_scaled_attention.argtypes = [p, i, p, p, p, ll, i, i, i, i, p, i, p, p, i, p, p, p, p,
-                                              p, i, p, p, i, i, i, i, i, i, i, p, p]
+                                              p, i, p, p, i, i, i, i, i, i, i, i, p, p]
+        lib.fsie_norm_rotate_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, p, p, f,
+                                               i, p, p]
+        lib.fsie_head_gate.argtypes = [p, i, p, i, i, i, i, i, p]
+        lib.fsie_scaled_sum_rmsnorm.argtypes = [p, p, f, p, f, p, p, p, i, i, f, i, i, p]
         lib.fsie_rotate_mix_write.argtypes = [p, i, p, p, i, p, p, p, ll, i, i, i, i, i, i, i, i, p, p,
                                               i, p, p]
         lib.fsie_latent_prep.argtypes = [p, i, p, p, i, p, p, ll, i, p, f, p, i, i, i, i, i, i, i, i, p, p]
         lib.fsie_head_product.argtypes = [p, ll, i, p, p, ll, i, i, i, i, i, i, p]
         for name in ("fsie_norm_add_norm", "fsie_gated_act", "fsie_mingru_scan",
                      "fsie_scaled_attention_rows", "fsie_scaled_attention", "fsie_rotate_mix_write",
-                     "fsie_latent_prep", "fsie_head_product"):
+                     "fsie_latent_prep", "fsie_head_product", "fsie_norm_rotate_write", "fsie_head_gate",
+                     "fsie_scaled_sum_rmsnorm"):
             getattr(lib, name).restype = i
         _mixers = lib
     return _mixers
@@ -1279,8 +1405,10 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
                      item_slots: Optional[torch.Tensor], out: torch.Tensor, tokens: int, heads: int,
                      kv_heads: int, window: int, error: torch.Tensor, nsplit: int = 1,
                      part_o: Optional[torch.Tensor] = None,
-                     part_ml: Optional[torch.Tensor] = None, form: str = "auto") -> torch.Tensor:
-    """Causal (optionally windowed) softmax attention of q [tokens, heads x key_dim] over paged keys
+                     part_ml: Optional[torch.Tensor] = None, form: str = "auto",
+                     chunk: int = 0) -> torch.Tensor:
+    """Causal (optionally windowed; `chunk` > 0: only over the keys j with j // chunk == i // chunk)
+    softmax attention of q [tokens, heads x key_dim] over paged keys
     [kv_head][slot][key_dim] and values [kv_head][slot][value_dim] (or, values_in_keys, the first
     value_dim columns of the key rows), scores multiplied by head_scale[head]; scores, softmax and
     weights in 32-bit.  `form`: "auto" takes a tensor-core kernel where one fits (bfloat16, key
@@ -1303,7 +1431,7 @@ def scaled_attention(q: torch.Tensor, q_ld: int, head_scale: torch.Tensor, k_pag
         value_dim, int(values_in_keys), _ptr(block_tables), block_tables.stride(0), _ptr(tile_item),
         _ptr(tile_row0), tiles, _ptr(item_qstart), _ptr(item_qlen), _ptr(item_pos0), _ptr(item_slots),
         _ptr(out), heads * value_dim, _ptr(part_o), _ptr(part_ml), tokens, heads, kv_heads, window,
-        nsplit, _tag(q.dtype), SCALED_ATTENTION_FORMS[form], _ptr(error), _stream()),
+        int(chunk), nsplit, _tag(q.dtype), SCALED_ATTENTION_FORMS[form], _ptr(error), _stream()),
         "scaled_attention")
     return out
 
@@ -1336,6 +1464,81 @@ def rotate_mix_write(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch
                                           page_stride, page_size, tokens, heads, kv_heads, dim, vdim,
                                           rotary_dim, mix_mode, _ptr(mix), _ptr(v_first),
                                           _tag(proj.dtype), _ptr(error), _stream()), "rotate_mix_write")
+
+
+def norm_rotate_write(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
+                      slot_of: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      page_stride: int, page_size: int, heads: int, kv_heads: int, dim: int, vdim: int,
+                      rotary_dim: int, q_gain: Optional[torch.Tensor], k_gain: Optional[torch.Tensor],
+                      eps: float, error: torch.Tensor) -> None:
+    """proj [tokens, q | k | v | ...]: every head of q (of k) divided by its root mean square (eps
+    inside the root) times q_gain (k_gain) [dim] in 32-bit where that gain is given; then q rotated in
+    place and k into its page over the first rotary_dim of each head (pairs i, i + rotary_dim / 2);
+    values into their page."""
+    _need(proj, None, "proj")
+    _need(positions, torch.int32, "positions")
+    _need(cos_sin, torch.float32, "cos_sin")
+    _need(slot_of, torch.int32, "slot_of")
+    tokens, ld = proj.shape
+    if rotary_dim > 0 and cos_sin.shape[-1] != rotary_dim:
+        raise KernelError("norm_rotate_write: cos/sin table width differs from rotary_dim")
+    if k_pages.dtype is not proj.dtype or v_pages.dtype is not proj.dtype:
+        raise KernelError("norm_rotate_write: cache dtype differs from the projection dtype")
+    for name, gain in (("q_gain", q_gain), ("k_gain", k_gain)):
+        if gain is not None:
+            _need(gain, torch.float32, name)
+            if gain.numel() != dim:
+                raise KernelError(f"norm_rotate_write: {name} must hold one number per column of a head")
+    _check(mixers().fsie_norm_rotate_write(_ptr(proj), ld, _ptr(positions), _ptr(cos_sin), cos_sin.shape[0],
+                                           _ptr(slot_of), _ptr(k_pages), _ptr(v_pages), page_stride,
+                                           page_size, tokens, heads, kv_heads, dim, vdim, rotary_dim,
+                                           _ptr(q_gain), _ptr(k_gain), float(eps), _tag(proj.dtype),
+                                           _ptr(error), _stream()), "norm_rotate_write")
+
+
+def head_gate(out: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int) -> torch.Tensor:
+    """out[t, h, :] <- out[t, h, :] * sigmoid(gate[t, h]); out [tokens, heads * vdim], `gate`
+    [tokens, heads] may be a view of columns of a wider tensor."""
+    _need(out, None, "out", contiguous=False)
+    _need(gate, out.dtype, "gate", contiguous=False)
+    tokens = out.shape[0]
+    if out.shape[1] != heads * vdim or gate.shape != (tokens, heads) or out.stride(1) != 1 or gate.stride(1) != 1:
+        raise KernelError("head_gate: shapes do not fit")
+    _check(mixers().fsie_head_gate(_ptr(out), out.stride(0), _ptr(gate), gate.stride(0), tokens, heads, vdim,
+                                   _tag(out.dtype), _stream()), "head_gate")
+    return out
+
+
+def scaled_sum_rmsnorm(x: torch.Tensor, deltas, scales, gain: Optional[torch.Tensor], eps: float,
+                       out: Optional[torch.Tensor], rows: Optional[torch.Tensor] = None,
+                       write_x: bool = True) -> Optional[torch.Tensor]:
+    """x (float32 residual) += scales[0] * deltas[0] + scales[1] * deltas[1] (one or two pending
+    outputs, in 32-bit); out = rmsnorm(x) * gain in out's dtype (gain float32).  With `rows` only
+    those rows are worked on (out row r from x row rows[r]); x is left untouched unless write_x."""
+    _need(x, torch.float32, "x")
+    hidden = x.shape[-1]
+    deltas, scales = tuple(deltas), tuple(float(v) for v in scales)
+    if not 1 <= len(deltas) <= 2 or len(scales) != len(deltas):
+        raise KernelError("scaled_sum_rmsnorm: one or two pending outputs, a scale for each")
+    for d in deltas:
+        _need(d, deltas[0].dtype, "delta")
+        if d.shape[-1] != hidden or d.numel() != x.numel():
+            raise KernelError("scaled_sum_rmsnorm: a pending output is not of x's shape")
+    count = x.numel() // hidden
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+        count = rows.numel()
+    if out is not None:
+        _need(out, deltas[0].dtype, "out")
+        _need(gain, torch.float32, "gain")
+        if out.numel() < count * hidden or gain.numel() != hidden:
+            raise KernelError("scaled_sum_rmsnorm: out or gain does not fit")
+    second = deltas[1] if len(deltas) > 1 else None
+    _check(mixers().fsie_scaled_sum_rmsnorm(_ptr(x), _ptr(deltas[0]), scales[0], _ptr(second),
+                                            scales[1] if second is not None else 0.0, _ptr(gain), _ptr(out),
+                                            _ptr(rows), count, hidden, float(eps), int(write_x),
+                                            _tag(deltas[0].dtype), _stream()), "scaled_sum_rmsnorm")
+    return out
 
 
 def latent_prep(proj: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
@@ -1396,11 +1599,11 @@ def routed():
         lib.fsie_logit_cap.argtypes = [p, ll, f, f, p]
         lib.fsie_sigmoid_gate.argtypes = [p, i, p, i, i, i, i, p]
         lib.fsie_moe_tile_rows.argtypes = []
-        lib.fsie_moe_route.argtypes = [p, i, p, p, p, p, p, i, i, i, i, i, i, f, i, i, i, p]
+        lib.fsie_moe_route.argtypes = [p, i, p, p, p, p, p, i, i, i, i, i, i, f, i, i, i, i, p]
         lib.fsie_moe_align.argtypes = [p, i, i, i, i, p, p, p, p, p, p, p]
         lib.fsie_moe_gather.argtypes = [p, ll, p, p, i, i, p, i, i, p]
         lib.fsie_moe_product.argtypes = [p, ll, p, p, ll, p, p, p, p, p, i, i, i, i, i, i, i, i, p]
-        lib.fsie_moe_combine.argtypes = [p, p, p, p, p, i, i, i, i, p]
+        lib.fsie_moe_combine.argtypes = [p, p, p, p, p, i, i, i, p, i, p, ll, i, p]
         for name in ("fsie_sum_layernorm", "fsie_settle_concat", "fsie_logit_cap", "fsie_sigmoid_gate",
                      "fsie_moe_tile_rows", "fsie_moe_route", "fsie_moe_align", "fsie_moe_gather", "fsie_moe_product",
                      "fsie_moe_combine"):
@@ -1498,10 +1701,11 @@ def moe_tile_rows() -> int:
 
 def moe_route(y: Optional[torch.Tensor], w_router: Optional[torch.Tensor], correction: Optional[torch.Tensor],
               ids: torch.Tensor, weights: torch.Tensor, top: int, groups: int, keep: int, scale: float,
-              scores: str = "sigmoid", normalise: bool = True, logits: Optional[torch.Tensor] = None) -> None:
+              scores: str = "sigmoid", normalise: bool = True, logits: Optional[torch.Tensor] = None,
+              group_score: str = "top2") -> None:
     """Per token: s = sigmoid (or softmax) of the router's logits in 32-bit; the `top` experts with the
-    largest s + correction among the `keep` best of `groups` groups (a group's score: its two
-    largest); weights s / (their sum + 1e-20) * scale.  The logits are w_router y, summed here
+    largest s + correction among the `keep` best of `groups` groups (a group's score: the sum of its
+    two largest s + correction, or - `group_score` "max" - the largest); weights s / (their sum + 1e-20) * scale.  The logits are w_router y, summed here
     (w_router float32 [experts, width]) or - `logits`, float32 [tokens, experts] - by a product
     before this call.  ids int32, weights float32, both [tokens, top]."""
     _need(ids, torch.int32, "ids")
@@ -1510,6 +1714,8 @@ def moe_route(y: Optional[torch.Tensor], w_router: Optional[torch.Tensor], corre
         _need(correction, torch.float32, "correction")
     if scores not in ("sigmoid", "softmax"):
         raise KernelError("moe_route: scores must be 'sigmoid' or 'softmax'")
+    if group_score not in ("top2", "max"):
+        raise KernelError("moe_route: group_score must be 'top2' or 'max'")
     if logits is not None:
         _need(logits, torch.float32, "logits")
         tokens, experts = logits.shape
@@ -1527,8 +1733,8 @@ def moe_route(y: Optional[torch.Tensor], w_router: Optional[torch.Tensor], corre
         raise KernelError("moe_route: shapes do not fit")
     _check(routed().fsie_moe_route(y_ptr, y_ld, w_ptr, _ptr(logits), _ptr(correction), _ptr(ids),
                                    _ptr(weights), tokens, width, experts, int(top), int(groups), int(keep),
-                                   float(scale), int(scores == "softmax"), int(normalise), tag,
-                                   _stream()), "moe_route")
+                                   float(scale), int(scores == "softmax"), int(normalise),
+                                   int(group_score == "max"), tag, _stream()), "moe_route")
 
 
 def moe_align(ids: torch.Tensor, pairs: int, experts: int, lists: torch.Tensor,
@@ -1578,10 +1784,13 @@ def moe_gather(x: torch.Tensor, lists, tile: int, top: int, out: torch.Tensor) -
 
 
 def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists, pairs: int, top: int,
-                gated: bool, activation: str = "silu") -> torch.Tensor:
+                gated: bool, activation: str = "silu", first: Optional[bool] = None) -> torch.Tensor:
     """The experts' products over the sorted pairs.  gated: weight [experts, 2 n, k] (gate rows, then up
     rows), x [tokens, k] read at pair // top, out [pairs, n] = f(gate) * up in sorted order.  Not gated:
-    weight [experts, n, k], x [pairs, k] in sorted order, out [pairs, n] at each pair's own row."""
+    weight [experts, n, k], x [pairs, k] in sorted order, out [pairs, n] at each pair's own row - or,
+    `first` (an expert without a gate: its first product), x [tokens, k] read at pair // top and
+    out [pairs, n] = f(x w^T) in sorted order."""
+    mode = 1 if gated else (2 if first else 0)
     _need(x, None, "x", contiguous=False)
     _need(weight, x.dtype, "weight")
     _need(out, x.dtype, "out")
@@ -1593,15 +1802,19 @@ def moe_product(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, lists,
         raise KernelError("moe_product: shapes do not fit")
     _check(routed().fsie_moe_product(_ptr(x), x.stride(0), _ptr(weight), _ptr(out), out.stride(0),
                                      _ptr(offsets), _ptr(order), _ptr(tile_expert), _ptr(tile_row0),
-                                     _ptr(meta), pairs, experts, int(top), n, k, int(gated),
+                                     _ptr(meta), pairs, experts, int(top), n, k, mode,
                                      GATE_KINDS[activation], _tag(x.dtype), _stream()), "moe_product")
     return out
 
 
 def moe_combine(expert_out: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor],
-                out: torch.Tensor, top: int, place: Optional[torch.Tensor] = None) -> torch.Tensor:
+                out: torch.Tensor, top: int, place: Optional[torch.Tensor] = None,
+                ids: Optional[torch.Tensor] = None, experts: int = 0,
+                y: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[t] = sum_j weights[t, j] * expert_out[t * top + j] (+ shared[t]), summed in 32-bit; with
-    `place` (int32 [tokens * top]) pair p's row of expert_out is place[p]."""
+    `place` (int32 [tokens * top]) pair p's row of expert_out is place[p].  With `ids` (int32
+    [tokens, top]), `experts` and `y` [tokens, width]: a choice at or beyond `experts` names an
+    identity expert, whose output is the token's row of y."""
     _need(expert_out, None, "expert_out")
     _need(weights, torch.float32, "weights")
     _need(out, expert_out.dtype, "out")
@@ -1614,6 +1827,14 @@ def moe_combine(expert_out: torch.Tensor, weights: torch.Tensor, shared: Optiona
         raise KernelError("moe_combine: shapes do not fit")
     if place is not None:
         _need(place, torch.int32, "place")
+    y_ld = 0
+    if ids is not None:
+        _need(ids, torch.int32, "ids")
+        _need(y, out.dtype, "y", contiguous=False)
+        if ids.numel() < tokens * top or y.shape != out.shape or y.stride(1) != 1:
+            raise KernelError("moe_combine: ids or y does not fit")
+        y_ld = y.stride(0)
     _check(routed().fsie_moe_combine(_ptr(expert_out), _ptr(weights), _ptr(shared), _ptr(place), _ptr(out),
-                                     tokens, width, int(top), _tag(out.dtype), _stream()), "moe_combine")
+                                     tokens, width, int(top), _ptr(ids), int(experts), _ptr(y), y_ld,
+                                     _tag(out.dtype), _stream()), "moe_combine")
     return out

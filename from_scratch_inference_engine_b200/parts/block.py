@@ -15,7 +15,8 @@ from .norm import LayerNorm, NormedDelta, PendingSum, RMSNorm
 
 @register_part("arrangement", "prenorm")
 class PreNormBlock(Part):
-    """x += mixer(norm(x)); x += feed_forward(norm(x))  (src/model/model.cpp:107-141).
+    """x += mixer(norm(x)); x += feed_forward(norm(x))  (src/model/model.cpp:107-141).  A layer may
+    have no feed-forward.
 
     The residual stream `x` is float32 and is updated in place.  A sublayer's output is
     not added at once: it is handed on as `delta` and added by the next norm kernel, which
@@ -26,20 +27,29 @@ class PreNormBlock(Part):
         self.prefix = prefix
         self.mixer_norm = build_part("norm", layer.mixer_norm, prefix + layer.mixer_norm_name)
         self.mixer = build_part("mixer", layer.mixer, prefix + layer.mixer_name)
-        self.feed_forward_norm = build_part("norm", layer.feed_forward_norm,
-                                            prefix + layer.feed_forward_norm_name)
-        self.feed_forward = build_part("feed_forward", layer.feed_forward,
-                                       prefix + layer.feed_forward_name)
+        self.feed_forward = self.feed_forward_norm = None
+        if layer.feed_forward is not None:          # a layer may have no feed-forward
+            self.feed_forward_norm = build_part("norm", layer.feed_forward_norm,
+                                                prefix + layer.feed_forward_norm_name)
+            self.feed_forward = build_part("feed_forward", layer.feed_forward,
+                                           prefix + layer.feed_forward_name)
+        # a checkpoint may still hold the norm of a feed-forward that the layer does not have
+        self.unused: List[TensorSpec] = []
+        if layer.feed_forward is None and layer.feed_forward_norm is not None:
+            import dataclasses
+            unused = build_part("norm", layer.feed_forward_norm, prefix + layer.feed_forward_norm_name)
+            self.unused = [dataclasses.replace(spec, optional=True) for spec in unused.tensor_specs()]
 
     def parts(self):
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm,
+                                  self.feed_forward) if part is not None]
 
     @property
     def capturable(self) -> bool:
         return all(part.capturable for part in self.parts())
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [spec for part in self.parts() for spec in part.tensor_specs()]
+        return [spec for part in self.parts() for spec in part.tensor_specs()] + self.unused
 
     def bind(self, tensors, runtime) -> None:
         self.runtime = runtime
@@ -51,7 +61,9 @@ class PreNormBlock(Part):
         ctx.residual_copy = None      # this block changes x without keeping a copy of it up to date
         # the normed rows are read by the sublayer that follows and by nothing after it
         y = self._normed(self.mixer_norm, x, delta, "prenorm.mixer_in")
-        mixed = self.mixer.forward(ctx, y, cache)
+        mixed = self.mixer.forward(ctx, y, cache)     # a tensor, or what the norms add as a whole
+        if self.feed_forward is None:
+            return mixed
         y = self._normed(self.feed_forward_norm, x, mixed, "prenorm.feed_forward_in")
         return self.feed_forward.forward(ctx, y)
 

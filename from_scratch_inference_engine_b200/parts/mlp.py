@@ -28,9 +28,9 @@ class SwiGluMlp(Part):
 
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, bias: bool = False,
                  names: Optional[Dict[str, str]] = None, activation: str = "silu"):
-        if activation not in ops.GATE_KINDS:
+        if activation not in ops.FUSED_GATES:
             raise ValueError(f"unknown gate activation '{activation}' "
-                             f"({', '.join(sorted(ops.GATE_KINDS))})")
+                             f"({', '.join(sorted(ops.FUSED_GATES))})")
         self.activation = activation
         self.prefix, self.hidden_size = prefix, int(hidden_size)
         self.intermediate_size = int(intermediate_size)

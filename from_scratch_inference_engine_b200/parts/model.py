@@ -16,7 +16,8 @@ from .base import LayerCache, StateNeed, build_part
 
 
 class DecoderModel:
-    """Embedding (times `embedding_scale`) -> blocks in the order of `spec.schedule`, an inlet
+    """Embedding (times `embedding_scale`, then through `embedding_norm` where the model has one)
+    -> blocks in the order of `spec.schedule`, an inlet
     before the calls that name one -> final norm -> head, times `logit_scale`, capped by
     `logit_softcap * tanh(. / logit_softcap)` where a cap is given.
 
@@ -32,6 +33,8 @@ class DecoderModel:
         self.blocks = [build_part("arrangement",
                                   _arrangement_spec(layer), layer.prefix) for layer in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        self.embedding_norm = None if spec.embedding_norm is None else \
+            build_part("norm", spec.embedding_norm, spec.embedding_norm_prefix)
         self.inlets = [build_part("inlet", part, prefix) for part, prefix in spec.inlets]
         self.inlet_before = [call.inlet for call in spec.schedule]
         self.embedding: Optional[torch.Tensor] = None
@@ -50,6 +53,8 @@ class DecoderModel:
             specs.append(TensorSpec("lm_head.weight", shape, optional=True,
                                     same_as=spec.embedding_name))
         specs += self.final_norm.tensor_specs()
+        if self.embedding_norm is not None:
+            specs += self.embedding_norm.tensor_specs()
         for inlet in self.inlets:
             specs += inlet.tensor_specs()
         for block in self.blocks:
@@ -74,6 +79,8 @@ class DecoderModel:
                      if self.spec.head_name is not None else self.embedding)
         runtime.prepare_weight(self.head)
         self.final_norm.bind(placed, runtime)
+        if self.embedding_norm is not None:
+            self.embedding_norm.bind(placed, runtime)
         for inlet in self.inlets:
             inlet.bind(placed, runtime)
         for block in self.blocks:
@@ -84,7 +91,8 @@ class DecoderModel:
     def capturable(self) -> bool:
         """Whether a step launches the same kernels whatever the data (every part says so)."""
         return self.final_norm.capturable and all(block.capturable for block in self.blocks) \
-            and all(inlet.capturable for inlet in self.inlets)
+            and all(inlet.capturable for inlet in self.inlets) \
+            and (self.embedding_norm is None or self.embedding_norm.capturable)
 
     def cache_needs(self) -> List[Optional[CacheNeed]]:
         """Need of each cache entry (index = position in the run order); None where the
@@ -118,7 +126,12 @@ class DecoderModel:
         hidden = self.spec.hidden_size
         x = rt.buffer("model.residual", ctx.num_tokens, hidden, torch.float32)
         scale = self.spec.embedding_scale
-        ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error, scale)
+        if self.embedding_norm is None:
+            ops.embed_gather(ctx.token_ids, self.embedding, x, ctx.error, scale)
+        else:           # the normed rows, still 32-bit, are the stream
+            rows = rt.buffer("model.embedding_rows", ctx.num_tokens, hidden, torch.float32)
+            ops.embed_gather(ctx.token_ids, self.embedding, rows, ctx.error, scale)
+            x = self.embedding_norm.forward(rows, None, tag="model.residual", out_dtype=torch.float32)
         x0 = None
         if self.inlets:                   # the embedding output, for the inlets that read it
             x0 = rt.buffer("model.embedding_output", ctx.num_tokens, hidden, torch.float32)

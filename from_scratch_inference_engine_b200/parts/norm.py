@@ -32,28 +32,44 @@ class PendingSum:
     deltas: tuple
 
 
+@dataclass
+class ScaledSum:
+    """The outputs of mixers that ran side by side on the same input, each with its weight, still
+    to be added to the residual stream (x += a1 d1 + a2 d2): the norm that runs next adds them in
+    32-bit, so the weighted sum is never rounded to the storage type."""
+
+    deltas: tuple
+    scales: tuple
+
+
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
-    """y = x * rsqrt(mean(x^2) + eps) * gain over the last axis, a plain gain (not 1 + gain),
-    statistics in 32-bit (reference: src/model/nn.cpp:45-72, 64-bit statistics there).
+    """y = x * rsqrt(mean(x^2) + eps) * gain over the last axis, statistics in 32-bit (reference:
+    src/model/nn.cpp:45-72, 64-bit statistics there).  The gain is the stored tensor, or - with
+    `one_plus`, a weight stored around zero - 1 + the stored tensor (summed in 32-bit at bind).
 
     forward adds `delta` into the float32 residual `x` first (one kernel, one pass over x).
     """
 
     capturable = True
 
-    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight"):
+    def __init__(self, prefix: str, width: int, eps: float, weight_name: str = "weight",
+                 one_plus: bool = False):
         self.prefix, self.width, self.eps = prefix, int(width), float(eps)
         self.name = prefix + weight_name
+        self.one_plus = bool(one_plus)
         self.gain: Optional[torch.Tensor] = None
         self._gain_f32: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> List[TensorSpec]:
-        return [TensorSpec(self.name, (self.width,), role="vector", init="gain")]
+        return [TensorSpec(self.name, (self.width,), role="vector",
+                           init="normal" if self.one_plus else "gain")]
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
         self.gain = tensors[self.name].contiguous()
+        if self.one_plus:
+            self.gain = (self.gain.to(torch.float32) + 1.0).contiguous()
         self._gain_f32 = None
 
     @property
@@ -63,13 +79,21 @@ class RMSNorm(Part):
             self._gain_f32 = self.gain.to(torch.float32).contiguous()
         return self._gain_f32
 
-    def forward(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta],
+    def forward(self, x: torch.Tensor, delta: Union[None, torch.Tensor, NormedDelta, ScaledSum],
                 rows: Optional[torch.Tensor] = None, write_x: bool = True,
-                tag: Optional[str] = None) -> torch.Tensor:
+                tag: Optional[str] = None, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         """`tag`: where the result may live (`Runtime.buffer`); None asks for fresh memory.
-        `delta` is added to x as it is, or - a `NormedDelta` - after its own RMS norm."""
+        `delta` is added to x as it is, or - a `NormedDelta` - after its own RMS norm, or - a
+        `ScaledSum` - as the weighted sum of its parts.  `out_dtype` float32 (nothing pending) gives
+        the normed rows in 32-bit: a norm whose result is itself the residual stream."""
         count = x.shape[0] if rows is None else rows.numel()
+        if out_dtype is torch.float32 and delta is None:
+            out = self.runtime.buffer(tag, count, self.width, torch.float32)
+            return ops.add_rmsnorm(x, None, self.gain_f32, self.eps, out, rows=rows, write_x=False)
         out = self.runtime.buffer(tag, count, self.width, self.runtime.dtype)
+        if isinstance(delta, ScaledSum):
+            return ops.scaled_sum_rmsnorm(x, delta.deltas, delta.scales, self.gain_f32, self.eps, out,
+                                          rows=rows, write_x=write_x)
         if isinstance(delta, NormedDelta):
             return ops.norm_add_norm(x, delta.delta, delta.gain, delta.eps, self.gain_f32, self.eps,
                                      out, rows=rows, write_x=write_x)

@@ -46,6 +46,24 @@ def yarn_rotary_table(theta: float, rotary_dim: int, length: int, factor: float,
     return (np.concatenate([np.cos(angles), np.sin(angles)], axis=1) * magnitude).astype(np.float32)
 
 
+def llama3_rotary_table(theta: float, rotary_dim: int, length: int, factor: float, original: float,
+                        low: float, high: float) -> np.ndarray:
+    """The table of `rotary_table` with the frequencies rescaled by wavelength: with l = 2 pi / f_i,
+    pair i keeps f_i where l < original / high, turns at f_i / factor where l > original / low, and
+    in between, with t = (original / l - low) / (high - low), at (1 - t) f_i / factor + t f_i.
+    64-bit on the host, rounded once."""
+    import math
+    half = rotary_dim // 2
+    inv_freq = np.power(float(theta), -2.0 * np.arange(half, dtype=np.float64) / rotary_dim)
+    wavelength = 2.0 * math.pi / inv_freq
+    blend = (original / wavelength - low) / (high - low) if high != low else np.ones_like(inv_freq)
+    mixed = (1.0 - blend) * inv_freq / factor + blend * inv_freq
+    scaled = np.where(wavelength < original / high, inv_freq,
+                      np.where(wavelength > original / low, inv_freq / factor, mixed))
+    angles = np.arange(length, dtype=np.float64)[:, None] * scaled[None, :]
+    return np.concatenate([np.cos(angles), np.sin(angles)], axis=1).astype(np.float32)
+
+
 @register_part("position", "rotary")
 class RotaryEncoding(Part):
     """Rotation of pairs over the first `rotary_dim` of each head: `pairing` "half" pairs
@@ -106,6 +124,34 @@ class YarnRotaryEncoding(RotaryEncoding):
              self.slow),
             lambda: torch.from_numpy(yarn_rotary_table(self.theta, self.rotary_dim, length, self.factor,
                                                        self.original, self.fast, self.slow)))
+
+
+@register_part("position", "llama3_rotary")
+class Llama3RotaryEncoding(RotaryEncoding):
+    """`rotary` with the frequencies rescaled by wavelength (`llama3_rotary_table`): `factor`, the
+    `original` length and the `low` and `high` numbers of turns within it between which a pair goes
+    over from stretched to kept.  The kernels read the table as they read the plain one."""
+
+    def __init__(self, prefix: str, theta: float, rotary_dim: int, factor: float, original: float,
+                 low: float, high: float, max_position: int = 0, pairing: str = "half"):
+        super().__init__(prefix, theta, rotary_dim, max_position, pairing)
+        if factor <= 0 or original <= 0 or low <= 0 or high <= 0 or theta <= 1:
+            raise ValueError("llama3_rotary: factor, original, low and high must be positive, theta above 1")
+        self.factor, self.original = float(factor), float(original)
+        self.low, self.high = float(low), float(high)
+
+    def bind(self, tensors, runtime) -> None:
+        self.runtime = runtime
+        length = max(self.max_position, runtime.max_positions, 1)
+        if self.rotary_dim == 0:
+            self.table = runtime.shared_table(("rotary-none",),
+                                              lambda: torch.zeros((1, 0), dtype=torch.float32))
+            return
+        self.table = runtime.shared_table(
+            ("llama3_rotary", self.theta, self.rotary_dim, length, self.factor, self.original, self.low,
+             self.high),
+            lambda: torch.from_numpy(llama3_rotary_table(self.theta, self.rotary_dim, length, self.factor,
+                                                         self.original, self.low, self.high)))
 
 
 @register_part("position", "none")

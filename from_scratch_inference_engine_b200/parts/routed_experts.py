@@ -15,13 +15,16 @@ from .base import Part, build_part, register_part
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(Part):
     """`experts` gated feed-forwards down(act(gate y) * (up y)) without biases, of which a token
-    uses `top`.
+    uses `top`.  `gated`=False: the experts have no gate, down(act(up y)); "relu2" (the square of
+    relu) is an activation for those.  `identity` > 0: the router has that many more outputs behind
+    the experts', each an expert whose output is its input y itself (times its weight); they have
+    no tensors, and they count as experts for the scores, the groups and the choice.
 
     Router: z = W_r y in 32-bit, s = sigmoid(z) (`scores` "softmax": softmax over the experts).
     The choice is made on s + correction (a stored vector, `correction`=False: none) and the
     weights on s without it.  The experts form `groups` equal groups of neighbours; a group's
-    score is the sum of its two largest choice values, and only experts of the `keep` best groups
-    can be chosen.  The `top` largest are taken; their weights are s / (their sum + 1e-20) * `scale`
+    score is the sum of its two largest choice values (`group_score` "max": the largest), and only
+    experts of the `keep` best groups can be chosen.  The `top` largest are taken; their weights are s / (their sum + 1e-20) * `scale`
     (`normalise`=False: s * scale).  The output is the weighted sum of the chosen experts' outputs,
     plus - with `shared` (any feed-forward part) - what that part gives for the token.
 
@@ -44,20 +47,29 @@ class RoutedExperts(Part):
     def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, experts: int, top: int,
                  groups: int = 1, keep: int = 1, scale: float = 1.0, scores: str = "sigmoid",
                  normalise: bool = True, correction: bool = True, activation: str = "silu",
-                 shared: Optional[PartSpec] = None, names: Optional[Dict[str, str]] = None):
-        if activation not in ops.GATE_KINDS:
-            raise ValueError(f"unknown gate activation '{activation}'")
+                 shared: Optional[PartSpec] = None, names: Optional[Dict[str, str]] = None,
+                 gated: bool = True, identity: int = 0, group_score: str = "top2"):
+        if activation not in (ops.FUSED_GATES if gated else ops.GATE_KINDS):
+            raise ValueError(f"unknown activation '{activation}' for experts "
+                             f"{'with' if gated else 'without'} a gate")
+        if group_score not in ("top2", "max"):
+            raise ValueError("group_score must be 'top2' or 'max'")
+        self.gated, self.identity, self.group_score = bool(gated), int(identity), group_score
+        if self.identity < 0:
+            raise ValueError("routed_experts: identity must not be negative")
         if scores not in ("sigmoid", "softmax"):
             raise ValueError("scores must be 'sigmoid' or 'softmax'")
         self.prefix, self.hidden_size = prefix, int(hidden_size)
         self.intermediate_size, self.experts, self.top = int(intermediate_size), int(experts), int(top)
         self.groups, self.keep, self.scale = int(groups), int(keep), float(scale)
         self.scores, self.normalise, self.activation = scores, bool(normalise), activation
-        if self.experts <= 0 or not 0 < self.top <= self.experts:
-            raise ValueError("routed_experts: top must lie in 1..experts")
-        if self.groups <= 0 or self.experts % self.groups or not 0 < self.keep <= self.groups:
-            raise ValueError("routed_experts: experts must divide into `groups` groups, keep in 1..groups")
-        if self.top > self.keep * (self.experts // self.groups):
+        self.routed = self.experts + self.identity        # outputs of the router
+        if self.experts <= 0 or not 0 < self.top <= self.routed:
+            raise ValueError("routed_experts: top must lie in 1..experts (+ identity)")
+        if self.groups <= 0 or self.routed % self.groups or not 0 < self.keep <= self.groups:
+            raise ValueError("routed_experts: experts (+ identity) must divide into `groups` groups, "
+                             "keep in 1..groups")
+        if self.top > self.keep * (self.routed // self.groups):
             raise ValueError("routed_experts: the kept groups hold fewer than `top` experts")
         self.has_correction = bool(correction)
         self.names = dict(self.NAMES)
@@ -77,20 +89,25 @@ class RoutedExperts(Part):
         h, f = self.hidden_size, self.intermediate_size
         specs = []
         for e in range(self.experts):
-            specs += [TensorSpec(self._expert(e, "gate"), (f, h)), TensorSpec(self._expert(e, "up"), (f, h)),
-                      TensorSpec(self._expert(e, "down"), (h, f))]
-        specs.append(TensorSpec(self.prefix + self.names["router"], (self.experts, h)))     # in the compute dtype
+            if self.gated:
+                specs.append(TensorSpec(self._expert(e, "gate"), (f, h)))
+            specs += [TensorSpec(self._expert(e, "up"), (f, h)), TensorSpec(self._expert(e, "down"), (h, f))]
+        specs.append(TensorSpec(self.prefix + self.names["router"], (self.routed, h)))     # in the compute dtype
         if self.has_correction:
-            specs.append(TensorSpec(self.prefix + self.names["correction"], (self.experts,), role="vector"))
+            specs.append(TensorSpec(self.prefix + self.names["correction"], (self.routed,), role="vector"))
         if self.shared is not None:
             specs += self.shared.tensor_specs()
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
-        self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")],
-                                                 tensors[self._expert(e, "up")]])
-                                      for e in range(self.experts)]).contiguous()
+        if self.gated:
+            self.w_gate_up = torch.stack([torch.cat([tensors[self._expert(e, "gate")],
+                                                     tensors[self._expert(e, "up")]])
+                                          for e in range(self.experts)]).contiguous()
+        else:           # the same name for the first matrix of an expert without a gate
+            self.w_gate_up = torch.stack([tensors[self._expert(e, "up")]
+                                          for e in range(self.experts)]).contiguous()
         self.w_down = torch.stack([tensors[self._expert(e, "down")]
                                    for e in range(self.experts)]).contiguous()
         self.w_router = tensors[self.prefix + self.names["router"]].contiguous()
@@ -102,8 +119,9 @@ class RoutedExperts(Part):
 
     def _grouped_weights(self):
         if self._grouped is None:
-            self._grouped = (ops.GroupedTiledWeight(self.w_gate_up, True, self.activation),
-                             ops.GroupedTiledWeight(self.w_down, False))
+            first = (ops.GroupedTiledWeight(self.w_gate_up, True, self.activation) if self.gated else
+                     ops.GroupedTiledWeight(self.w_gate_up, False, plain_activation=self.activation))
+            self._grouped = (first, ops.GroupedTiledWeight(self.w_down, False))
         return self._grouped
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
@@ -114,10 +132,14 @@ class RoutedExperts(Part):
         weights = rt.buffer("routed.weights", tokens, top, torch.float32)
         logits = rt.linear_f32_out(y, self.w_router, "routed.logits")
         ops.moe_route(None, None, self.correction, ids, weights, top, self.groups, self.keep,
-                      self.scale, self.scores, self.normalise, logits=logits)
+                      self.scale, self.scores, self.normalise, logits=logits, group_score=self.group_score)
+        # choices at or beyond `experts` are identity experts: no rows in the products, and the
+        # weighted sum takes the token's own row for them
+        identity = dict(ids=ids, experts=self.experts, y=y) if self.identity else {}
         shared = None if self.shared is None else self.shared.forward(ctx, y)
         out = rt.buffer("routed.out", tokens, self.hidden_size, y.dtype)
         grouped = (y.dtype is torch.bfloat16 and rt.products == "own"
+                   and (self.gated or self.activation == "relu2")
                    and pairs >= self.GROUPED_MIN_ROWS * self.experts
                    and self.hidden_size % 8 == 0 and self.intermediate_size % 8 == 0
                    and y.stride(0) % 8 == 0 and y.data_ptr() % 16 == 0)
@@ -134,12 +156,12 @@ class RoutedExperts(Part):
             ops.gemm_tiles_grouped(gate_up, x_sorted, act, lists[2], lists[4], ctx.error, rt.sm_count)
             expert_out = rt.buffer("routed.expert_out", rows, self.hidden_size, y.dtype)
             ops.gemm_tiles_grouped(down, act, expert_out, lists[2], lists[4], ctx.error, rt.sm_count)
-            return ops.moe_combine(expert_out, weights, shared, out, top, place=lists[5])
+            return ops.moe_combine(expert_out, weights, shared, out, top, place=lists[5], **identity)
         lists = ops.moe_align(ids, pairs, self.experts,
                               rt.buffer("routed.lists", 1, ops.moe_lists_size(pairs, self.experts),
                                         torch.int32).view(-1))
         act = rt.buffer("routed.act", pairs, self.intermediate_size, y.dtype)
-        ops.moe_product(y, self.w_gate_up, act, lists, pairs, top, True, self.activation)
+        ops.moe_product(y, self.w_gate_up, act, lists, pairs, top, self.gated, self.activation, first=True)
         expert_out = rt.buffer("routed.expert_out", pairs, self.hidden_size, y.dtype)
         ops.moe_product(act, self.w_down, expert_out, lists, pairs, top, False)
-        return ops.moe_combine(expert_out, weights, shared, out, top)
+        return ops.moe_combine(expert_out, weights, shared, out, top, **identity)
