@@ -117,9 +117,9 @@ def turn_frequencies(rot):
 
 def turn(x, positions, rot):
     """x [tokens, heads, dim]: the first `dims` columns of every head, pairs (i, i + dims/2)."""
-    dims = int(rot["dims"])
-    if dims == 0:
+    if not rot or not int(rot["dims"]):
         return x
+    dims = int(rot["dims"])
     half = dims // 2
     angle = positions.to(F64)[:, None] * turn_frequencies(rot)[None, :]
     c, s = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
