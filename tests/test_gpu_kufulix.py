@@ -118,12 +118,13 @@ def test_heads_normed_then_turned_into_the_cache(dtype, normed):
     table = torch.from_numpy(llama3_rotary_table(50.0, dims, 64, 4.0, 32, 1.0, 4.0)).cuda()
     slots = torch.tensor([7, 2, 30, 12, 5, 21, -1, 0, 19], dtype=torch.int32)
     pages = 8
-    k_pages = torch.zeros(pages, kv_heads * page * dim, device="cuda", dtype=dtype)
-    v_pages = torch.zeros(pages, kv_heads * page * vdim, device="cuda", dtype=dtype)
+    # a page holds its keys and then its values, as the engine lays them out
+    both = torch.zeros(pages, kv_heads * page * (dim + vdim), device="cuda", dtype=dtype)
+    k_pages, v_pages = both[:, :kv_heads * page * dim], both[:, kv_heads * page * dim:]
     work = proj.clone().cuda()
     error = torch.zeros(1, dtype=torch.int32, device="cuda")
     ops.norm_rotate_write(work, positions.int().cuda(), table, slots.cuda(), k_pages, v_pages,
-                          k_pages.stride(0), page, heads, kv_heads, dim, vdim, dims,
+                          both.stride(0), page, heads, kv_heads, dim, vdim, dims,
                           q_gain.cuda() if normed else None, k_gain.cuda() if normed else None, eps, error)
     assert int(error.item()) == 0
     q = proj[:, :heads * dim].double().view(tokens, heads, dim)
@@ -137,8 +138,8 @@ def test_heads_normed_then_turned_into_the_cache(dtype, normed):
     got_q = work[:, :heads * dim].cpu().double().view(tokens, heads, dim)
     assert (got_q - q).abs().max() < tolerance * max(1.0, float(q.abs().max()))
     assert torch.equal(work[:, width:].cpu(), proj[:, width:])
-    kp = k_pages.cpu().double().view(pages, kv_heads, page, dim)
-    vp = v_pages.cpu().double().view(pages, kv_heads, page, vdim)
+    kp = k_pages.cpu().double().reshape(pages, kv_heads, page, dim)
+    vp = v_pages.cpu().double().reshape(pages, kv_heads, page, vdim)
     for t, slot in enumerate(slots.tolist()):
         if slot < 0:
             continue
