@@ -24,7 +24,9 @@ A step is one decode step of a batch of 8 requests whose contexts end at 4,096 t
 `--workload hybrid` measures the Metulix hybrid design beside the Qwen2 model of equal width, heads,
 feed-forward, depth and window (prefill of one prompt, decode steps of a batch, ms per kind of kernel);
 `--workload zadepel` does the same for the Zadepel design (latent attention, grouped-query attention with
-blended values, minGRU) beside Qwen2 with full causal attention; `--workload tapalix` measures the
+blended values, minGRU) beside Qwen2 with full causal attention; `--workload kufulix` measures the
+Kufulix design (windowed attention beside a state-space mixer, chunked attention with gated heads, experts
+without gates) beside a Metulix model of equal size; `--workload tapalix` measures the
 Tapalix design (latent attention with and without a rotated part, routed experts beside a shared one,
 a looped stretch of layers) beside a Zadepel model of latent attention layers with a dense feed-forward
 of the width a token uses, at equal depth.
@@ -479,6 +481,46 @@ def tapalix_shapes(width, heads, dim, rope, rank, experts, top, groups, keep, ff
     return tapalix, zadepel
 
 
+# sizes of the Kufulix comparison: (name, width, heads, kv heads, head size, state-space heads, their
+# value size, state size, experts, identity experts, top, groups, kept groups, expert ff, layers, vocab)
+KUFULIX_SIZES = (("w2048", 2048, 16, 4, 128, 32, 64, 128, 32, 4, 4, 6, 4, 1024, 4, 32000),
+                 ("w4096", 4096, 32, 8, 128, 64, 64, 128, 16, 2, 2, 3, 2, 2048, 4, 32000))
+
+
+def kufulix_shapes(width, heads, kv_heads, dim, ss_heads, ss_vdim, state, experts, identity, top, groups, keep,
+                   ff, layers, vocab, window):
+    """A Kufulix model (a windowed attention with normed q and k beside a state-space mixer, then a
+    chunked attention with gated heads, then both again on the first two layers' tensors; every
+    layer with routed experts without gates and with identity experts) and the closest model the
+    engine had: a Metulix model of lightning layers (as many state numbers per request as the
+    state-space mixer keeps) and windowed attention layers in turn, with a dense feed-forward as
+    wide as what a Kufulix token uses (top x expert ff)."""
+    mlp = {"kind": "moe", "expert": {"ff": ff},
+           "router": {"experts": experts, "identity": identity, "top": top,
+                      "groups": {"count": groups, "keep": keep}}}
+    rot = {"base": 10000.0, "dims": dim // 2,
+           "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "rot": rot}
+    parallel = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": dict(attention, mask={"size": window}),
+        "right": {"heads": ss_heads, "vdim": ss_vdim, "state": state, "groups": 1, "conv": 4, "norm_groups": 1},
+        "left_scale": 0.7, "right_scale": 1.2}}
+    chunked = {"type": "attention", "mlp": mlp, "mixer": dict(attention, mask={"size": 2 * window})}
+    order = (parallel, chunked, dict(parallel, weights_of=0), dict(chunked, weights_of=1))
+    kufulix = {"architecture": "Kufulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "logit_softcap": 30.0, "layers": [order[i] if i < 2 else order[2 + i % 2] for i in range(layers)]}
+    lightning_heads = ss_heads * ss_vdim * state // (dim * dim)
+    lightning = {"type": "lightning", "mlp": {"kind": "dense", "ff": top * ff}, "mixer": {
+        "heads": lightning_heads, "dim": dim, "vdim": dim,
+        "decay": [1.0 - 2.0 ** -(3 + 5 * h / lightning_heads) for h in range(lightning_heads)]}}
+    windowed = {"type": "attention", "mlp": {"kind": "dense", "ff": top * ff}, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "conv": 4, "scale": dim ** -0.5,
+        "rot": {"base": 10000.0, "dims": dim}, "mask": {"size": window, "keep_first": 0}}}
+    metulix = {"architecture": "Metulix", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+               "layers": [lightning if i % 2 == 0 else windowed for i in range(layers)]}
+    return kufulix, metulix
+
+
 def hybrid_workload(args, design="metulix") -> int:
     """The Metulix design (or, `design`, the Zadepel design) beside the Qwen2 model of equal size
     (random bf16 weights): prefill of
@@ -515,7 +557,9 @@ def hybrid_workload(args, design="metulix") -> int:
                                "talking_attention_mma", "norm_add_norm", "gated_act", "mingru_scan",
                                "scaled_attention", "rotate_mix_write", "latent_prep", "head_product",
                                "sum_layernorm", "settle_concat", "logit_cap", "sigmoid_gate", "moe_route",
-                               "moe_align", "moe_gather", "moe_product", "gemm_tiles_grouped", "moe_combine")
+                               "moe_align", "moe_gather", "moe_product", "gemm_tiles_grouped", "moe_combine",
+                               "ssd_prep", "ssd_tails", "ssd_gate_norm", "norm_rotate_write", "head_gate",
+                               "scaled_sum_rmsnorm")
              if hasattr(ops, name)]
 
     def by_kind(fn):
@@ -551,7 +595,7 @@ def hybrid_workload(args, design="metulix") -> int:
         out["(whole step)"] = total
         return {k: round(v, 4) for k, v in sorted(out.items(), key=lambda kv: -kv[1])}
 
-    table = TAPALIX_SIZES if design == "tapalix" else HYBRID_SIZES
+    table = {"tapalix": TAPALIX_SIZES, "kufulix": KUFULIX_SIZES}.get(design, HYBRID_SIZES)
     sizes = [s for s in table if not args.sizes or s[0] in args.sizes.split(",")]
     results = []
     clocks = ClockSampler()
@@ -567,6 +611,17 @@ def hybrid_workload(args, design="metulix") -> int:
                      "expert_ff": ff, "shared_ff": shared, "layers": layers, "passes": times,
                      "layer_runs": len(shapes[1]["layers"]), "vocab": vocab}
             beside = "zadepel"
+        elif design == "kufulix":
+            (name, width, heads, kv_heads, dim, ss_heads, ss_vdim, state, experts, identity, top, groups, keep,
+             ff, layers, vocab) = size
+            layers = args.layers or layers
+            shapes = kufulix_shapes(width, heads, kv_heads, dim, ss_heads, ss_vdim, state, experts, identity,
+                                    top, groups, keep, ff, layers, vocab, window)
+            entry = {"size": name, "width": width, "heads": heads, "kv_heads": kv_heads, "head_dim": dim,
+                     "state_space": {"heads": ss_heads, "vdim": ss_vdim, "state": state},
+                     "experts": experts, "identity": identity, "top": top, "groups": [groups, keep],
+                     "expert_ff": ff, "layers": layers, "vocab": vocab, "window": window, "chunk": 2 * window}
+            beside = "metulix"
         else:
             name, width, heads, kv_heads, dim, ff, layers, vocab = size
             layers = args.layers or layers
@@ -642,7 +697,7 @@ def hybrid_workload(args, design="metulix") -> int:
     clock_record = clocks.stop()
     print(json.dumps({
         "metric": f"prefill and decode tokens/s of the {design.capitalize()} design beside "
-                  f"{'Zadepel' if design == 'tapalix' else 'Qwen2'} at equal size",
+                  f"{ {'tapalix': 'Zadepel', 'kufulix': 'Metulix'}.get(design, 'Qwen2') } at equal size",
         "impl": "engine", "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "dtype": "bf16" if compute == "bfloat16" else "fp32",
         "config": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context,
@@ -732,7 +787,7 @@ def main() -> int:
                              "blocks it falls to instead of sharing it out among all (for measuring that choice)")
     parser.add_argument("--fp32-steps", type=int, default=8,
                         help="decode steps timed on the float32 path after the bf16 run (0 = skip)")
-    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid", "zadepel", "tapalix"],
+    parser.add_argument("--workload", default="decode", choices=["decode", "serving", "long", "timeline", "hybrid", "zadepel", "tapalix", "kufulix"],
                         help="decode: the default measurement; serving: continuous batching of 256 "
                              "requests at the 1.5B shape; long: the 14B shape, decode at batch 32 with "
                              "8,192-token contexts and chunked prefill of an 8,192-token prompt; "
@@ -767,6 +822,8 @@ def main() -> int:
         return hybrid_workload(args, design="zadepel")
     if args.workload == "tapalix":
         return hybrid_workload(args, design="tapalix")
+    if args.workload == "kufulix":
+        return hybrid_workload(args, design="kufulix")
 
     import numpy as np
     import torch
