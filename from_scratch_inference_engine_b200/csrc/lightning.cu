@@ -51,7 +51,8 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
                       const float* __restrict__ decay, float* __restrict__ out, int heads, int dim,
                       int vdim, const int* __restrict__ seg_item, const int* __restrict__ seg_row0,
                       int seg_tokens, float* __restrict__ chunk_states, int phase, int share,
-                      const float* __restrict__ decay_tok, long long state_stride) {
+                      const float* __restrict__ decay_tok, long long state_stride,
+                      float* __restrict__ chunk_decay) {
     constexpr int PAD = DR >= 4 ? DR + 4 : DR;
     constexpr int ROW_LEN = SCAN_ROW_GROUPS * PAD;
     __shared__ __align__(16) float qs[SCAN_TOKENS * ROW_LEN];
@@ -78,6 +79,7 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
                               : chunk_states + (((size_t)blockIdx.z * heads + head) * dim) * vdim);
     const float head_decay = decay ? decay[head] : 1.f;
     const int qk_head = head / share;                  // `share` heads read the same q and k columns
+    float through = 1.f;                               // the product of the chunk's decays (phase 1)
     float s[DR][4];
 #pragma unroll
     for (int i = 0; i < DR; ++i) {
@@ -126,6 +128,7 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
         __syncthreads();
         for (int t = 0; t < n; ++t) {
             const float lambda = ls[t];
+            through *= lambda;
             const float4 v4 = *reinterpret_cast<const float4*>(vs + t * SCAN_COLS + cg * 4);
             const float v[4] = {v4.x, v4.y, v4.z, v4.w};
             float kk[DR], qq[DR];
@@ -174,6 +177,8 @@ lightning_scan_kernel(const float* __restrict__ proj, int ld, int q_off, int k_o
             }
         }
     }
+    if (phase == 1 && chunk_decay && blockIdx.x == 0 && threadIdx.x == 0)
+        chunk_decay[(size_t)blockIdx.z * heads + head] = through;
     if (phase != 2 && col0 < vdim) {
 #pragma unroll
         for (int i = 0; i < DR; ++i) {
@@ -213,7 +218,7 @@ __global__ void lightning_chain_kernel(const int* __restrict__ item_qstart, cons
                                        const int* __restrict__ item_slots,
                                        int items, float* __restrict__ state, const float* __restrict__ decay,
                                        float* __restrict__ chunk_states, int seg_tokens, int heads,
-                                       int dim, int vdim, const float* __restrict__ decay_tok,
+                                       int dim, int vdim, const float* __restrict__ chunk_decay,
                                        long long state_stride) {
     const int item = blockIdx.y;
     const int slot = item_slots[item];
@@ -227,7 +232,6 @@ __global__ void lightning_chain_kernel(const int* __restrict__ item_qstart, cons
     const int chunks = (count + seg_tokens - 1) / seg_tokens;
     const int head = (int)(e / per_head);
     const float lambda = decay ? decay[head] : 1.f;
-    const float* per_token = decay_tok ? decay_tok + (size_t)item_qstart[item] * heads + head : nullptr;
     float s = state[(size_t)slot * state_stride + e];
     for (int c = 0; c < chunks; ++c) {
         const int len = min(seg_tokens, count - c * seg_tokens);
@@ -235,8 +239,8 @@ __global__ void lightning_chain_kernel(const int* __restrict__ item_qstart, cons
         const float sum = *at;
         *at = s;
         float power = 1.f;                                 // decay^len by the same products as the scan
-        for (int t = 0; t < len; ++t)
-            power *= per_token ? per_token[(size_t)(c * seg_tokens + t) * heads] : lambda;
+        if (chunk_decay) power = chunk_decay[(size_t)(first + c) * heads + head];     // (what the chunk's walk multiplied)
+        else for (int t = 0; t < len; ++t) power *= lambda;
         s = power * s + sum;
     }
     state[(size_t)slot * state_stride + e] = s;
@@ -287,7 +291,8 @@ int fsie_silu_rows(const void* proj, int ld, int width, float* act, int tokens, 
 // heads * vdim] (float).
 //
 // With seg_item / seg_row0 (num_segs chunks of seg_tokens tokens, listed request by request) and
-// chunk_states [num_segs, heads, dim, vdim] the requests run chunk-parallel in three launches.
+// chunk_states [num_segs, heads, dim, vdim] (with decay_tok: and num_segs * heads floats more) the
+// requests run chunk-parallel in three launches.
 int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_off,
                         const int* item_qstart, const int* item_qlen, const int* item_slots,
                         int items, float* state, const float* decay, float* out, int heads,
@@ -302,6 +307,8 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
     const bool chunked = seg_item != nullptr;
     if (chunked && (!seg_row0 || !chunk_states || num_segs <= 0 || num_segs > 65535 || seg_tokens <= 0))
         return ERR_BAD_ARGUMENT;
+    // decays per token: every chunk's walk leaves the product of its decays behind its sums, for the chain
+    float* chunk_decay = chunked && decay_tok ? chunk_states + (size_t)num_segs * heads * dim * vdim : nullptr;
     dim3 grid((vdim + SCAN_COLS - 1) / SCAN_COLS, heads, chunked ? num_segs : items);
     int phase = chunked ? 1 : 0;
     const int threads = SCAN_COLS / 4 * SCAN_ROW_GROUPS;
@@ -311,7 +318,7 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
     launch_code = launch_dependent(lightning_scan_kernel<DPT>, grid, threads, 0, stream,         \
         proj, ld, q_off, k_off, v_off, item_qstart, item_qlen, item_slots, state,      \
         decay, out, heads, dim, vdim, seg_item, seg_row0, seg_tokens, chunk_states, phase, share, \
-        decay_tok, state_stride)
+        decay_tok, state_stride, chunk_decay)
 #define FSIE_SCAN_BY_SIZE(T)                                                                     \
     do {                                                                                         \
         if (per_thread <= 1) FSIE_SCAN(T, 1);                                                    \
@@ -327,7 +334,7 @@ int fsie_lightning_scan(const float* proj, int ld, int q_off, int k_off, int v_o
         const size_t per_state = (size_t)heads * dim * vdim;
         lightning_chain_kernel<<<dim3((unsigned)((per_state + 255) / 256), items), 256, 0, stream>>>(
             item_qstart, item_qlen, item_slots, items, state, decay, chunk_states, seg_tokens, heads, dim, vdim,
-            decay_tok, state_stride);
+            chunk_decay, state_stride);
         code = FSIE_LAUNCH_CHECK();
         if (code) return code;
         phase = 2;

@@ -5,7 +5,8 @@
 KERNEL: attention_decode, attention_prefill, add_rmsnorm, rope_kv_write, swiglu, argmax,
 sample, linear (the library product as the engine calls it), gemm_f32, gemm_decode,
 gemm_decode_swiglu, gemm_tiles, gemm_tiles_swiglu (the engine's own tcgen05 products),
-sum_layernorm, routed_experts (every kernel of a feed-forward of routed experts, one line for all).
+sum_layernorm, routed_experts (every kernel of a feed-forward of routed experts, one line for all),
+state_space (every kernel of a state-space mixer, and the same scan with one decay per head beside it).
 
 Each kernel is timed with CUDA events over --iters launches after --warmup launches; between
 launches a buffer larger than L2 is read so that inputs come from HBM (read, not written:
@@ -241,6 +242,75 @@ def run_routed_experts(args, timer, dtype):
                            "kernels": rows}, **extra)))
 
 
+def run_state_space(args, timer, dtype):
+    """Every kernel between the two products of a state-space mixer for one prompt of --tokens
+    tokens: --heads heads of --head-dim value columns over --state state rows, one group, four taps;
+    and `lightning_scan` with one decay per head over as many state numbers (heads of 128 x 128), the
+    like kernel of decaying linear attention.  ms, achieved rates, and the share of the measured copy
+    rate (the scan: of the nominal 32-bit FMA peak, 4 flops per state number and token)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    rand = lambda *shape: torch.randn(shape, generator=g, device="cuda", dtype=torch.float32)
+    elem = 2 if dtype is torch.bfloat16 else 4
+    tokens, heads, vdim, state, taps = args.tokens, args.heads, args.head_dim, args.state, 4
+    inner, channels = heads * vdim, heads * vdim + 2 * state
+    width = 2 * inner + 2 * state + heads
+    proj = (rand(tokens, width) * 0.5).to(dtype)
+    matrix = heads * state * vdim
+    floats = -(-(matrix + (taps - 1) * channels) // 4) * 4
+    slots = torch.zeros(1, floats, device="cuda")
+    conv, conv_b = rand(channels, taps) * 0.5, rand(channels) * 0.1
+    dt_bias, a_log, skip, gain = rand(heads), torch.linspace(-4.0, 0.5, heads, device="cuda"), rand(heads), rand(inner)
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    qstart, qlen, slot = dev([0]), dev([tokens]), dev([0])
+    act = torch.empty(tokens, channels + inner, device="cuda")
+    decay = torch.empty(tokens, heads, device="cuda")
+    o = torch.empty(tokens, inner, device="cuda")
+    y = torch.empty(tokens, inner, dtype=dtype, device="cuda")
+    chunk = 64
+    segs = -(-tokens // chunk)
+    chunks = {}
+    if tokens > 2 * chunk:
+        chunks = dict(seg_item=dev([0] * segs), seg_row0=dev([i * chunk for i in range(segs)]), num_segs=segs,
+                      seg_tokens=chunk, chunk_states=torch.empty(segs * (matrix + heads), device="cuda"))
+    peak = peaks()
+    ffma = 148 * 128 * 2 * 1.965e9 / 1e12
+    rows = []
+
+    def note(name, ms, nbytes, flops):
+        gbs, tflops = nbytes / (ms * 1e-3) / 1e9, flops / (ms * 1e-3) / 1e12
+        rows.append({"kernel": name, "ms": round(ms, 5), "GB/s": round(gbs, 1), "TFLOP/s": round(tflops, 2),
+                     "frac_hbm": round(gbs / peak["hbm_gbs"], 3), "frac_ffma": round(tflops / ffma, 3)})
+
+    note("ssd_prep", timer(lambda: ops.ssd_prep(proj, inner, inner + channels, qstart, qlen, slot, 1, slots, matrix,
+                                                conv, conv_b, dt_bias, a_log, heads, vdim, act, decay)),
+         tokens * ((channels + heads) * elem + (channels + inner + heads) * 4), 2.0 * tokens * channels * taps)
+    note("ssd_tails", timer(lambda: ops.ssd_tails(proj, inner, channels, taps, qstart, qlen, slot, 1, slots, matrix)),
+         2 * (taps - 1) * channels * 4, 0.0)
+    scan_bytes = tokens * (inner + 2 * state + heads + inner) * 4 * (2 if chunks else 1)
+    note("lightning_scan, decay per token", timer(lambda: ops.lightning_scan(
+        act, inner + state, inner, channels, qstart, qlen, slot, 1, slots, None, o, heads, state, vdim,
+        share=heads, decay_tok=decay, **chunks)), scan_bytes, 4.0 * tokens * matrix)
+    note("ssd_gate_norm", timer(lambda: ops.ssd_gate_norm(o, act, proj, 0, skip, gain, y, vdim, 1, 1e-6)),
+         tokens * inner * (8 + 2 * elem), 8.0 * tokens * inner)
+    # the like kernel: one decay per head, heads of 128 x 128 over as many state numbers
+    dim = 128
+    like_heads = max(1, matrix // (dim * dim))
+    like = rand(tokens, 3 * like_heads * dim)
+    like_state = torch.zeros(1, like_heads, dim, dim, device="cuda")
+    like_decay = torch.linspace(0.9, 0.999, like_heads, device="cuda")
+    like_out = torch.empty(tokens, like_heads * dim, device="cuda")
+    like_chunks = dict(chunks)
+    if chunks:
+        like_chunks["chunk_states"] = torch.empty(segs * like_heads * dim * dim, device="cuda")
+    note("lightning_scan, decay per head", timer(lambda: ops.lightning_scan(
+        like, 0, like_heads * dim, 2 * like_heads * dim, qstart, qlen, slot, 1, like_state, like_decay, like_out,
+        like_heads, dim, dim, **like_chunks)),
+         tokens * 4 * like_heads * dim * 4 * (2 if chunks else 1), 4.0 * tokens * like_heads * dim * dim)
+    print(json.dumps({"kernel": "state_space", "dtype": args.dtype, "tokens": tokens, "heads": heads, "vdim": vdim,
+                      "state": state, "taps": taps, "chunk_parallel": bool(chunks), "peaks": peak["source"],
+                      "kernels": rows}))
+
+
 def run(args):
     timer = Timer(args.warmup, args.iters, not args.no_flush)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
@@ -335,6 +405,8 @@ def run(args):
         nbytes, flops = (m * k + n * k + m * n) * elem, 2.0 * m * n * k
     elif args.kernel == "routed_experts":
         return run_routed_experts(args, timer, dtype)
+    elif args.kernel == "state_space":
+        return run_state_space(args, timer, dtype)
     elif args.kernel == "sum_layernorm":
         x, d1, d2 = rand(args.tokens, args.hidden), rand(args.tokens, args.hidden).to(dtype), \
             rand(args.tokens, args.hidden).to(dtype)
@@ -374,6 +446,7 @@ def main(argv=None) -> int:
     parser.add_argument("--n", type=int, default=37888)
     parser.add_argument("--k", type=int, default=3584)
     parser.add_argument("--nsplit", type=int, default=0, help="0 = the engine's choice")
+    parser.add_argument("--state", type=int, default=128, help="state_space: state rows per head")
     parser.add_argument("--experts", type=int, default=64)
     parser.add_argument("--top", type=int, default=6)
     parser.add_argument("--groups", type=int, default=8)

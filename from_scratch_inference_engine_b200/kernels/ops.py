@@ -980,7 +980,8 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
     column groups of `dim`).
 
     With `seg_item` / `seg_row0` (int32, one entry per chunk of `seg_tokens` tokens, listed
-    request by request) and `chunk_states` (float32, num_segs * heads * dim * vdim at least) the
+    request by request) and `chunk_states` (float32, num_segs * heads * dim * vdim at least; with
+    `decay_tok` num_segs * heads more) the
     chunks of long prompts run side by side: each sums its own tokens, the sums are chained into
     the state at every chunk's start, and each chunk runs again from there for its outputs."""
     _need(proj, torch.float32, "proj")
@@ -1010,7 +1011,7 @@ def lightning_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
         _need(seg_item, torch.int32, "seg_item")
         _need(seg_row0, torch.int32, "seg_row0")
         _need(chunk_states, torch.float32, "chunk_states")
-        if chunk_states.numel() < num_segs * heads * dim * vdim:
+        if chunk_states.numel() < num_segs * heads * (dim * vdim + (decay_tok is not None)):
             raise KernelError("lightning_scan: chunk_states is too small")
     _check(scan().fsie_lightning_scan(_ptr(proj), ld, q_off, k_off, v_off, _ptr(item_qstart),
                                       _ptr(item_qlen), _ptr(item_slots), items, _ptr(state),

@@ -110,7 +110,7 @@ class StateSpaceDuality(Mixer):
             chunks = dict(seg_item=tiles.item, seg_row0=tiles.row0, num_segs=tiles.count,
                           seg_tokens=self.CHUNK_TOKENS,
                           chunk_states=ctx.scratch("state_space.chunk_states",
-                                                   tiles.count * self.matrix_floats))
+                                                   tiles.count * (self.matrix_floats + self.heads)))
         o = rt.buffer("state_space.o", tokens, inner, torch.float32)
         # q = C, k = B, v = dt * x; the heads of a group share its B and C
         ops.lightning_scan(act, inner + gn, inner, self.channels, ctx.item_qstart, ctx.item_qlen,

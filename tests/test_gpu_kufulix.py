@@ -296,7 +296,7 @@ def test_state_space_steps_carry_state_between_calls(dtype, heads, vdim, state, 
                     item.append(i)
                     row0.append(r)
             chunks = dict(seg_item=dev(item), seg_row0=dev(row0), num_segs=len(item), seg_tokens=64,
-                          chunk_states=torch.empty(len(item) * matrix, device="cuda"))
+                          chunk_states=torch.empty(len(item) * (matrix + heads), device="cuda"))
         o = torch.empty(tokens, inner, device="cuda")
         ops.lightning_scan(act, inner + gn, inner, channels, qstart, qlen, slot, 2, slots, None, o, heads,
                            state, vdim, share=heads // groups, decay_tok=decay, **chunks)
