@@ -22,7 +22,10 @@ __device__ __forceinline__ float ssd_softplus(float z) { return z > 20.f ? z : l
 constexpr int SSD_MAX_TAPS = 16;
 
 // One block per token.  act [tokens, act_ld] = [ c (channels) | dt x (inner) ]; decay [tokens, heads].
-template <typename T>
+// VEC: channels, the head size, the offsets and the row strides are multiples of 8 and the rows start
+// on 16 bytes: a thread owns eight neighbouring channels (all of one head), 16-byte loads per tap;
+// the weights then come from conv_wt [taps, channels], the transposed table.
+template <typename T, bool VEC>
 __global__ void ssd_prep_kernel(const T* __restrict__ proj, int ld, int conv_off, int dt_off,
                                 const int* __restrict__ item_qstart, const int* __restrict__ item_qlen,
                                 const int* __restrict__ item_slots, int items,
@@ -30,7 +33,7 @@ __global__ void ssd_prep_kernel(const T* __restrict__ proj, int ld, int conv_off
                                 const float* __restrict__ conv_w, const float* __restrict__ conv_b, int taps,
                                 int channels, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
                                 int heads, int vdim, float* __restrict__ act, int act_ld,
-                                float* __restrict__ decay) {
+                                float* __restrict__ decay, const float* __restrict__ conv_wt) {
     extern __shared__ float ssd_dt[];                  // [heads]
     __shared__ int found;
     grid_dependency_wait();
@@ -56,6 +59,34 @@ __global__ void ssd_prep_kernel(const T* __restrict__ proj, int ld, int conv_off
     const float* tail = state + (size_t)slot * state_stride + tail_off;     // [taps - 1][channels], oldest first
     const int inner = heads * vdim;
     float* out = act + (size_t)t * act_ld;
+    if (VEC) {
+        for (int c = threadIdx.x * 8; c < channels; c += blockDim.x * 8) {
+            float sum[8], u[8], w[8];
+            if (conv_b) load8(conv_b + c, sum);
+            else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] = 0.f;
+            }
+            for (int j = 0; j < taps; ++j) {
+                const int back = taps - 1 - j;
+                if (back <= r) load8(proj + (size_t)(t - back) * ld + conv_off + c, u);
+                else load8(tail + (size_t)(taps - 1 + r - back) * channels + c, u);
+                load8(conv_wt + (size_t)j * channels + c, w);         // the taps' weights, tap by tap
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] = fmaf(w[i], u[i], sum[i]);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[i] = ssd_silu(sum[i]);
+            store8(out + c, sum);
+            if (c < inner) {
+                const float dt = ssd_dt[c / vdim];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) sum[i] *= dt;
+                store8(out + channels + c, sum);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < channels; c += blockDim.x) {
         float sum = conv_b ? conv_b[c] : 0.f;
         const float* w = conv_w + (size_t)c * taps;
@@ -138,27 +169,32 @@ int fsie_ssd_max_taps() { return SSD_MAX_TAPS; }
 
 // proj [tokens, ld] of the storage type; state [slots, state_stride] float, a request's inputs of
 // the last taps - 1 tokens at tail_off; conv_w [channels, taps], conv_b [channels] or null, dt_bias,
-// a_log [heads] float; act [tokens, act_ld >= channels + heads * vdim] and decay [tokens, heads] float.
+// a_log [heads] float; act [tokens, act_ld >= channels + heads * vdim] and decay [tokens, heads] float;
+// conv_wt [taps, channels] float or null: conv_w transposed, for the form that takes eight channels at once.
 int fsie_ssd_prep(const void* proj, int ld, int conv_off, int dt_off, const int* item_qstart,
                   const int* item_qlen, const int* item_slots, int items, const float* state,
                   long long state_stride, long long tail_off, const float* conv_w, const float* conv_b,
                   int taps, int channels, const float* dt_bias, const float* a_log, int heads, int vdim,
-                  float* act, int act_ld, float* decay, int tokens, int dtype, cudaStream_t stream) {
+                  float* act, int act_ld, float* decay, const float* conv_wt, int tokens, int dtype,
+                  cudaStream_t stream) {
     if (tokens <= 0 || items <= 0) return 0;
     if (taps < 1 || taps > SSD_MAX_TAPS || channels < heads * vdim || heads <= 0 || vdim <= 0 ||
         act_ld < channels + heads * vdim || (taps > 1 && !state))
         return ERR_BAD_ARGUMENT;
-    const int threads = channels >= 2048 ? 512 : (channels >= 512 ? 256 : 128);
     const size_t smem = (size_t)heads * sizeof(float);
     if (smem > 40 * 1024) return ERR_UNSUPPORTED;
-    if (dtype == DTYPE_F32)
-        return launch_dependent(ssd_prep_kernel<float>, tokens, threads, smem, stream, (const float*)proj, ld,
-                                conv_off, dt_off, item_qstart, item_qlen, item_slots, items, state, state_stride,
-                                tail_off, conv_w, conv_b, taps, channels, dt_bias, a_log, heads, vdim, act,
-                                act_ld, decay);
-    return launch_dependent(ssd_prep_kernel<bf16>, tokens, threads, smem, stream, (const bf16*)proj, ld, conv_off,
-                            dt_off, item_qstart, item_qlen, item_slots, items, state, state_stride, tail_off,
-                            conv_w, conv_b, taps, channels, dt_bias, a_log, heads, vdim, act, act_ld, decay);
+    const bool vec = conv_wt && channels % 8 == 0 && vdim % 8 == 0 && conv_off % 8 == 0 && ld % 8 == 0 && act_ld % 8 == 0 &&
+        (taps == 1 || (state_stride % 8 == 0 && tail_off % 8 == 0)) &&
+        ((((size_t)proj) | ((size_t)act) | ((size_t)state) | ((size_t)conv_b) | ((size_t)conv_wt)) & 31) == 0;
+    const int threads = vec ? (channels >= 2048 ? 256 : (channels >= 1024 ? 128 : 64))
+                            : (channels >= 2048 ? 512 : (channels >= 512 ? 256 : 128));
+#define FSIE_SSD_PREP(T, V)                                                                                        \
+    launch_dependent(ssd_prep_kernel<T, V>, tokens, threads, smem, stream, (const T*)proj, ld, conv_off, dt_off,    \
+                     item_qstart, item_qlen, item_slots, items, state, state_stride, tail_off, conv_w, conv_b, taps, \
+                     channels, dt_bias, a_log, heads, vdim, act, act_ld, decay, conv_wt)
+    if (dtype == DTYPE_F32) return vec ? FSIE_SSD_PREP(float, true) : FSIE_SSD_PREP(float, false);
+    return vec ? FSIE_SSD_PREP(bf16, true) : FSIE_SSD_PREP(bf16, false);
+#undef FSIE_SSD_PREP
 }
 
 int fsie_ssd_tails(const void* proj, int ld, int conv_off, const int* item_qstart, const int* item_qlen,

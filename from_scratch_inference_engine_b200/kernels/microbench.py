@@ -256,9 +256,10 @@ def run_state_space(args, timer, dtype):
     width = 2 * inner + 2 * state + heads
     proj = (rand(tokens, width) * 0.5).to(dtype)
     matrix = heads * state * vdim
-    floats = -(-(matrix + (taps - 1) * channels) // 4) * 4
+    floats = -(-(matrix + (taps - 1) * channels) // 8) * 8
     slots = torch.zeros(1, floats, device="cuda")
     conv, conv_b = rand(channels, taps) * 0.5, rand(channels) * 0.1
+    conv_by_tap = conv.t().contiguous()
     dt_bias, a_log, skip, gain = rand(heads), torch.linspace(-4.0, 0.5, heads, device="cuda"), rand(heads), rand(inner)
     dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     qstart, qlen, slot = dev([0]), dev([tokens]), dev([0])
@@ -282,7 +283,8 @@ def run_state_space(args, timer, dtype):
                      "frac_hbm": round(gbs / peak["hbm_gbs"], 3), "frac_ffma": round(tflops / ffma, 3)})
 
     note("ssd_prep", timer(lambda: ops.ssd_prep(proj, inner, inner + channels, qstart, qlen, slot, 1, slots, matrix,
-                                                conv, conv_b, dt_bias, a_log, heads, vdim, act, decay)),
+                                                conv, conv_b, dt_bias, a_log, heads, vdim, act, decay,
+                                                conv_wt=conv_by_tap)),
          tokens * ((channels + heads) * elem + (channels + inner + heads) * 4), 2.0 * tokens * channels * taps)
     note("ssd_tails", timer(lambda: ops.ssd_tails(proj, inner, channels, taps, qstart, qlen, slot, 1, slots, matrix)),
          2 * (taps - 1) * channels * 4, 0.0)

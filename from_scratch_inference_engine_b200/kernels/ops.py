@@ -859,7 +859,7 @@ def scan():
         lib.fsie_gated_rmsnorm.argtypes = [p, p, i, i, p, p, i, i, f, i, p]
         lib.fsie_ssd_max_taps.argtypes = []
         lib.fsie_ssd_prep.argtypes = [p, i, i, i, p, p, p, i, p, ll, ll, p, p, i, i, p, p, i, i, p, i, p,
-                                      i, i, p]
+                                      p, i, i, p]
         lib.fsie_ssd_tails.argtypes = [p, i, i, p, p, p, i, p, ll, ll, i, i, i, p]
         lib.fsie_ssd_gate_norm.argtypes = [p, p, i, p, i, i, p, p, p, i, i, i, i, f, i, p]
         for name in ("fsie_lightning_scan", "fsie_silu_rows", "fsie_gated_rmsnorm", "fsie_ssd_max_taps",
@@ -1030,14 +1030,17 @@ def ssd_prep(proj: torch.Tensor, conv_off: int, dt_off: int, item_qstart: torch.
              item_qlen: torch.Tensor, item_slots: torch.Tensor, items: int,
              state: Optional[torch.Tensor], tail_off: int, conv_w: torch.Tensor,
              conv_b: Optional[torch.Tensor], dt_bias: torch.Tensor, a_log: torch.Tensor, heads: int,
-             vdim: int, act: torch.Tensor, decay: torch.Tensor) -> None:
+             vdim: int, act: torch.Tensor, decay: torch.Tensor,
+             conv_wt: Optional[torch.Tensor] = None) -> None:
     """What a state-space mixer's scan reads, per token of proj [tokens, ld] (the stored projection
     with the convolution's input columns at conv_off and the step sizes at dt_off):
     act [tokens, channels + heads * vdim] float32 = [silu(causal convolution + bias) | dt * x] with x
     the first heads * vdim convolved columns, dt = softplus(dt + dt_bias), and decay [tokens, heads]
     = exp(-exp(a_log) * dt).  conv_w float32 [channels, taps], the last column the current token's;
     the inputs of the taps - 1 tokens before a step's first live in the request's slot of `state`
-    [slots, n] (float32) from float tail_off on, oldest first (`ssd_tails` moves them on)."""
+    [slots, n] (float32) from float tail_off on, oldest first (`ssd_tails` moves them on).  conv_wt:
+    conv_w transposed ([taps, channels], contiguous), with which sizes in multiples of 8 take eight
+    channels per thread."""
     _need(proj, None, "proj")
     _need(conv_w, torch.float32, "conv_w")
     _need(dt_bias, torch.float32, "dt_bias")
@@ -1050,6 +1053,10 @@ def ssd_prep(proj: torch.Tensor, conv_off: int, dt_off: int, item_qstart: torch.
             act.shape[0] < tokens or decay.numel() < tokens * heads or dt_bias.numel() != heads or \
             a_log.numel() != heads or (conv_b is not None and conv_b.numel() != channels):
         raise KernelError("ssd_prep: shapes do not fit")
+    if conv_wt is not None:
+        _need(conv_wt, torch.float32, "conv_wt")
+        if tuple(conv_wt.shape) != (taps, channels):
+            raise KernelError("ssd_prep: conv_wt is not conv_w transposed")
     stride = 0
     if taps > 1:
         _need(state, torch.float32, "state", contiguous=False)
@@ -1059,8 +1066,8 @@ def ssd_prep(proj: torch.Tensor, conv_off: int, dt_off: int, item_qstart: torch.
     _check(scan().fsie_ssd_prep(_ptr(proj), ld, conv_off, dt_off, _ptr(item_qstart), _ptr(item_qlen),
                                 _ptr(item_slots), items, _ptr(state), stride, tail_off, _ptr(conv_w),
                                 _ptr(conv_b), taps, channels, _ptr(dt_bias), _ptr(a_log), heads, vdim,
-                                _ptr(act), act.stride(0), _ptr(decay), tokens, _tag(proj.dtype),
-                                _stream()), "ssd_prep")
+                                _ptr(act), act.stride(0), _ptr(decay), _ptr(conv_wt), tokens,
+                                _tag(proj.dtype), _stream()), "ssd_prep")
 
 
 def ssd_tails(proj: torch.Tensor, conv_off: int, channels: int, taps: int, item_qstart: torch.Tensor,

@@ -74,11 +74,13 @@ class StateSpaceDuality(Mixer):
 
     def state_need(self) -> Optional[StateNeed]:
         floats = self.matrix_floats + (self.taps - 1) * self.channels
-        return StateNeed((-(-floats // 4) * 4,), torch.float32)      # slots start on 16 bytes
+        return StateNeed((-(-floats // 8) * 8,), torch.float32)      # slots start on 32 bytes
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime) -> None:
         self.runtime = runtime
         p, n = self.prefix, self.names
+        if self.state > 256:
+            raise ValueError(f"state_space_duality: {self.state} state rows per head, the scan holds 256")
         if self.taps > ops.ssd_max_taps():
             raise ValueError(f"state_space_duality: {self.taps} taps, the kernels hold {ops.ssd_max_taps()}")
 
@@ -87,6 +89,7 @@ class StateSpaceDuality(Mixer):
         self.w_in = tensors[p + n["in"]].contiguous()
         self.w_o = tensors[p + n["o"]].contiguous()
         self.conv, self.conv_bias = vector("conv"), vector("conv_bias")
+        self.conv_by_tap = self.conv.t().contiguous()          # [taps, channels]: eight channels' weights in a row
         self.dt_bias, self.a_log, self.skip, self.gain = (vector("dt_bias"), vector("a_log"),
                                                           vector("skip"), vector("norm"))
         runtime.prepare_weight(self.w_in)
@@ -102,7 +105,8 @@ class StateSpaceDuality(Mixer):
         decay = rt.buffer("state_space.decay", tokens, self.heads, torch.float32)
         items = (ctx.item_qstart, ctx.item_qlen, ctx.item_slots, ctx.num_items)
         ops.ssd_prep(proj, inner, inner + self.channels, *items, cache.state, self.matrix_floats,
-                     self.conv, self.conv_bias, self.dt_bias, self.a_log, self.heads, self.vdim, act, decay)
+                     self.conv, self.conv_bias, self.dt_bias, self.a_log, self.heads, self.vdim, act, decay,
+                     conv_wt=self.conv_by_tap)
         ops.ssd_tails(proj, inner, self.channels, self.taps, *items, cache.state, self.matrix_floats)
         chunks = {}
         if int(ctx.h_qlen.max()) > 2 * self.CHUNK_TOKENS:

@@ -92,13 +92,13 @@ CONFIGS = {
                  state_space(3, 5, 7, groups=3, conv=4, norm_groups=3), 0.6, 1.1, mlp=moe(10, 3, 2, identity=3, groups=(3, 2))),
         chunked(attention(3, 3, 10, 6, 5, rot(500.0, 4)), mlp=moe(14, 7, 4, identity=1, groups=(2, 1)))],
         softcap=20.0),
-    # head sizes of real models in small: the tensor-core attention takes the chunked layer,
-    # long portions take the experts' grouped product
+    # head sizes of real models in small: the tensor-core attention takes the windowed and the
+    # chunked layers, long portions take the experts' grouped product
     "wide": model(150, 128, 1e-6, [
-        parallel(attention(4, 2, 64, 32, 40, rot(10000.0, 32, (8.0, 1.0, 4.0, 64))),
+        parallel(attention(4, 2, 64, 64, 40, rot(10000.0, 32, (8.0, 1.0, 4.0, 64))),
                  state_space(4, 32, 32, groups=2, conv=4), 0.7, 1.2, mlp=moe(64, 8, 2, identity=4, groups=(3, 2))),
         chunked(attention(4, 1, 64, 64, 48, rot(500000.0, 64, (4.0, 1.0, 4.0, 128))), mlp=moe(32, 4, 2)),
-        again(parallel(attention(4, 2, 64, 32, 40, rot(10000.0, 32, (8.0, 1.0, 4.0, 64))),
+        again(parallel(attention(4, 2, 64, 64, 40, rot(10000.0, 32, (8.0, 1.0, 4.0, 64))),
                        state_space(4, 32, 32, groups=2, conv=4), 0.7, 1.2,
                        mlp=moe(64, 8, 2, identity=4, groups=(3, 2))), 0)],
         softcap=14.0),

@@ -286,7 +286,8 @@ def test_state_space_steps_carry_state_between_calls(dtype, heads, vdim, state, 
         act = torch.empty(tokens, channels + inner, device="cuda")
         decay = torch.empty(tokens, heads, device="cuda")
         ops.ssd_prep(proj, inner, inner + channels, qstart, qlen, slot, 2, slots, matrix, f32["p.conv"],
-                     f32["p.conv.b"], f32["p.dt_bias"], f32["p.A_log"], heads, vdim, act, decay)
+                     f32["p.conv.b"], f32["p.dt_bias"], f32["p.A_log"], heads, vdim, act, decay,
+                     conv_wt=f32["p.conv"].t().contiguous() if call else None)      # both forms of the kernel
         ops.ssd_tails(proj, inner, channels, taps, qstart, qlen, slot, 2, slots, matrix)
         chunks = {}
         if max(counts) > 128:

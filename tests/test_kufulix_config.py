@@ -31,9 +31,9 @@ def test_layers_that_run_other_layers_tensors_are_calls_of_those_layers():
     assert needs[0] == needs[2] == needs[4] and needs[1] == needs[3] and needs[0] != needs[1]
     assert (needs[0].kv_heads, needs[0].head_dim, needs[0].v_dim, needs[0].window) == (3, 16, 8, 21)
     assert (needs[1].kv_heads, needs[1].head_dim, needs[1].v_dim, needs[1].window) == (2, 8, 16, 13)
-    # the matrices of four heads and the inputs of three earlier tokens, on a 16-byte border
+    # the matrices of four heads and the inputs of three earlier tokens, on a 32-byte border
     floats = 4 * 8 * 8 + 3 * (4 * 8 + 2 * 2 * 8)
-    assert states[0].shape == (-(-floats // 4) * 4,) and states[1] is None and states[2] == states[0]
+    assert states[0].shape == (-(-floats // 8) * 8,) and states[1] is None and states[2] == states[0]
     assert spec.logit_softcap == 12.0 and spec.embedding_norm is not None
 
 
