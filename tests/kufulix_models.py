@@ -109,8 +109,8 @@ def write_model(root, name, seed=0, std=0.08, sharpen=True) -> Path:
     """A folder with config.json and random weights for CONFIGS[name].  The state-space mixers'
     decays are spread from slow to fast over the heads (A_log from -4 to 0.5) and their step sizes
     drawn wide, so that some heads remember hundreds of tokens and others a few.  With `sharpen` the
-    routers' corrections are drawn wide (choices are made among negative values too, and the order
-    of the choice differs from the order of the weights), the routers ten times as wide (every
+    routers' corrections are spread wide and shuffled (choices are made among negative values too, and
+    the order of the choice differs from the order of the weights), the routers four times as wide (every
     token chooses its own experts), and the query and key projections - where they are normed, the
     norms' gains - three times as wide, so that scores spread and single keys stand out.  Without
     it the routers are drawn narrow and the corrections are 4 x 2^k with every k once: no rounding
@@ -126,12 +126,16 @@ def write_model(root, name, seed=0, std=0.08, sharpen=True) -> Path:
     for key in list(tensors):
         last = key.split(".")[-1]
         if last == "correction" and sharpen:
-            tensors[key] = torch.randn(tensors[key].shape, generator=generator).to(torch.bfloat16)
+            # spread evenly and shuffled: no two experts share a value after rounding to bfloat16 (a
+            # shared value would leave the choice between them to score differences below 32-bit rounding)
+            count = tensors[key].numel()
+            spread = torch.linspace(-0.4, 0.4, count) if count > 1 else torch.zeros(1)
+            tensors[key] = spread[torch.randperm(count, generator=generator)].to(torch.bfloat16)
         elif last == "correction":
             order = torch.randperm(tensors[key].numel(), generator=generator)
             tensors[key] = (4.0 * torch.pow(2.0, order.float())).to(torch.bfloat16)
         elif last == "router":
-            tensors[key] = (tensors[key].float() * (10.0 if sharpen else 0.3)).to(torch.bfloat16)
+            tensors[key] = (tensors[key].float() * (4.0 if sharpen else 0.3)).to(torch.bfloat16)
         elif last == "A_log":
             tensors[key] = torch.linspace(-4.0, 0.5, tensors[key].numel()).to(torch.bfloat16)
         elif last == "dt_bias":
@@ -142,3 +146,64 @@ def write_model(root, name, seed=0, std=0.08, sharpen=True) -> Path:
             tensors[key] = (tensors[key].float() * 3.0).to(torch.bfloat16)
     save_file(tensors, folder / "model.safetensors")
     return folder
+
+
+def random_config(seed: int) -> dict:
+    """A configuration drawn at random: two to five layers of either type, some of them running an
+    earlier layer's tensors, every size, mask, rotation, scale and router drawn anew."""
+    import random
+    rng = random.Random(seed)
+
+    def draw_attention():
+        kv_heads = rng.choice([1, 2, 3])
+        heads = kv_heads * rng.choice([1, 2, 4])
+        dim = rng.choice([6, 8, 16, 24, 32, 64])
+        vdim = rng.choice([4, 8, 10, 16, 32, 64])
+        dims = rng.choice([0, 2, dim // 2 // 2 * 2, dim // 2 * 2])
+        rotation = None
+        if dims:
+            scaling = rng.choice([None, (rng.choice([2.0, 4.0, 8.0]), 1.0, rng.choice([2.0, 4.0]), rng.choice([8, 16, 64]))])
+            rotation = rot(rng.choice([20.0, 1000.0, 500000.0]), dims, scaling)
+        return attention(heads, kv_heads, dim, vdim, rng.choice([1, 3, 7, 16, 21, 40, 64, 100]), rotation,
+                         scale=rng.choice([None, 0.3, 1.0]))
+
+    def draw_state_space():
+        groups = rng.choice([1, 2])
+        heads = groups * rng.choice([1, 2, 3])
+        vdim = rng.choice([4, 5, 8, 16, 32])
+        parts = rng.choice([p for p in (1, 2, 3, 4) if (heads * vdim) % p == 0])
+        return state_space(heads, vdim, rng.choice([3, 4, 8, 16, 33]), groups, rng.choice([1, 2, 3, 4]), parts)
+
+    def draw_mlp():
+        if rng.random() < 0.2:
+            return None
+        experts, identity = rng.choice([1, 3, 4, 6, 8]), rng.choice([0, 0, 1, 2, 4])
+        routed = experts + identity
+        groups = None
+        counts = [c for c in (2, 3, 4) if routed % c == 0]
+        if counts and rng.random() < 0.6:
+            count = rng.choice(counts)
+            groups = (count, rng.randint(1, count))
+        room = routed if groups is None else groups[1] * (routed // groups[0])
+        return moe(rng.choice([8, 12, 16, 40]), experts, rng.randint(1, min(room, 4)), identity, groups)
+
+    layers = []
+    for index in range(rng.randint(2, 5)):
+        if layers and rng.random() < 0.3:
+            source = rng.choice([i for i, layer in enumerate(layers) if "weights_of" not in layer])
+            layers.append(again(layers[source], source))
+        elif rng.random() < 0.6:
+            layers.append(parallel(draw_attention(), draw_state_space(), rng.choice([0.5, 1.0, 1.3]),
+                                   rng.choice([0.7, 1.0, 1.5]), mlp=draw_mlp()))
+        else:
+            layers.append(chunked(draw_attention(), mlp=draw_mlp()))
+    return model(rng.choice([50, 97, 128]), rng.choice([24, 36, 64, 128]), rng.choice([1e-5, 1e-6]), layers,
+                 softcap=rng.choice([0.0, 8.0, 30.0]))
+
+
+def write_random(root, seed: int, sharpen=True) -> Path:
+    CONFIGS[f"random{seed}"] = random_config(seed)
+    try:
+        return write_model(root, f"random{seed}", seed=seed, sharpen=sharpen)
+    finally:
+        pass

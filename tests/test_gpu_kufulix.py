@@ -692,3 +692,19 @@ def test_trace_replay_program_runs_the_design(tmp_path_factory, tmp_path, dtype,
     rows = helpers.collect_rows(steps, outputs)
     assert len(rows) == sum(len(ids) for ids in requests.values())
     assert_rows(rows, requests, folder, bound)
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 5, 8, 13])
+def test_configurations_drawn_at_random(tmp_path_factory, seed):
+    """Layer orders, sizes, masks, rotations, routers and shared tensors drawn at random (fixed seeds),
+    in float32: a whole prompt, portions beside decoded tokens of another request, and a tail token by
+    token, against the plain implementation."""
+    folder = km.write_random(tmp_path_factory.mktemp(f"kufulix_random{seed}"), seed)
+    vocab = km.CONFIGS[f"random{seed}"]["vocab"]
+    requests = {"a": helpers.random_ids(vocab, 150, seed), "b": helpers.random_ids(vocab, 41, seed + 1),
+                "c": helpers.random_ids(vocab, 67, seed + 2)}
+    runner = runner_for(folder, "float32", num_pages=24)
+    for steps in (helpers.trace_whole(requests), helpers.trace_mixed(requests, seed=seed, max_live=3),
+                  helpers.trace_tail_by_one({"b": requests["b"]}, tail=30)):
+        rows = helpers.run_trace_in_process(runner, steps)
+        assert_rows(rows, requests, folder, F32_BOUND)
