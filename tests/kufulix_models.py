@@ -202,8 +202,6 @@ def random_config(seed: int) -> dict:
 
 
 def write_random(root, seed: int, sharpen=True) -> Path:
+    """A folder for `random_config(seed)`, which is entered into CONFIGS as "random<seed>"."""
     CONFIGS[f"random{seed}"] = random_config(seed)
-    try:
-        return write_model(root, f"random{seed}", seed=seed, sharpen=sharpen)
-    finally:
-        pass
+    return write_model(root, f"random{seed}", seed=seed, sharpen=sharpen)
