@@ -39,16 +39,18 @@ MIXERS = ("parallel", "attention")
 
 def _check_attention(where: str, mixer: Mapping[str, Any]) -> None:
     heads = _integer(where, mixer, "heads")
-    kv_heads = _integer(where, mixer, "kv_heads")
+    kv_heads = _integer(where, mixer, "kv_heads") if "kv_heads" in mixer else heads
     if heads % kv_heads:
         raise ConfigError(f"config.json: {where}.heads must be a multiple of kv_heads")
     dim = _integer(where, mixer, "dim")
-    _integer(where, mixer, "vdim")
+    if "vdim" in mixer:
+        _integer(where, mixer, "vdim")
     _number(where, mixer, "scale")
     mask = mixer.get("mask")
-    if not isinstance(mask, Mapping):
-        raise ConfigError(f"config.json: {where}.mask must be an object with 'size'")
-    _integer(where + ".mask", mask, "size")
+    if mask is not None:            # absent or null: every earlier position is seen
+        if not isinstance(mask, Mapping):
+            raise ConfigError(f"config.json: {where}.mask must be an object with 'size', or null")
+        _integer(where + ".mask", mask, "size")
     rot = mixer.get("rot")
     if rot is None:
         return
@@ -73,9 +75,9 @@ def _check_state_space(where: str, mixer: Mapping[str, Any]) -> None:
     heads = _integer(where, mixer, "heads")
     vdim = _integer(where, mixer, "vdim")
     _integer(where, mixer, "state")
-    groups = _integer(where, mixer, "groups")
+    groups = _integer(where, mixer, "groups") if "groups" in mixer else 1
     _integer(where, mixer, "conv")
-    parts = _integer(where, mixer, "norm_groups")
+    parts = _integer(where, mixer, "norm_groups") if "norm_groups" in mixer else 1
     if heads % groups:
         raise ConfigError(f"config.json: {where}.heads must be a multiple of groups")
     if (heads * vdim) % parts:
@@ -173,8 +175,9 @@ class KufulixConfig:
                     if not isinstance(mixer.get(side), Mapping):
                         raise ConfigError(f"config.json: {where}.mixer.{side} must be an object")
                     check(f"{where}.mixer.{side}", mixer[side])
-                _number(where + ".mixer", mixer, "left_scale")
-                _number(where + ".mixer", mixer, "right_scale")
+                for key in ("left_scale", "right_scale"):        # absent: 1
+                    if key in mixer:
+                        _number(where + ".mixer", mixer, key)
             if layer.get("mlp") is not None:
                 _check_mlp(where + ".mlp", layer["mlp"])
             source = layer.get("weights_of")
@@ -209,10 +212,11 @@ class KufulixConfig:
     def _attention(self, mixer: Mapping[str, Any], windowed: bool) -> PartSpec:
         """`windowed`: the mask is a sliding window and q and k are normed per head (the left
         mixer of a parallel layer); else the mask is a chunk and the heads' outputs are gated."""
-        size = int(mixer["mask"]["size"])
+        size = int(mixer["mask"]["size"]) if mixer.get("mask") else 0
         return PartSpec("scaled_gqa_attention", {
-            "hidden_size": self.width, "heads": int(mixer["heads"]), "kv_heads": int(mixer["kv_heads"]),
-            "dim": int(mixer["dim"]), "vdim": int(mixer["vdim"]), "scale": float(mixer["scale"]),
+            "hidden_size": self.width, "heads": int(mixer["heads"]),
+            "kv_heads": int(mixer.get("kv_heads", mixer["heads"])),
+            "dim": int(mixer["dim"]), "vdim": int(mixer.get("vdim", mixer["dim"])), "scale": float(mixer["scale"]),
             "position": self._position(mixer.get("rot")), "temperature": False, "value_mix": "none",
             "window": size if windowed else 0, "chunk": 0 if windowed else size,
             "qk_norm": windowed, "eps": self.eps, "head_gate": not windowed})
@@ -220,8 +224,8 @@ class KufulixConfig:
     def _state_space(self, mixer: Mapping[str, Any]) -> PartSpec:
         return PartSpec("state_space_duality", {
             "hidden_size": self.width, "heads": int(mixer["heads"]), "vdim": int(mixer["vdim"]),
-            "state": int(mixer["state"]), "groups": int(mixer["groups"]), "taps": int(mixer["conv"]),
-            "norm_groups": int(mixer["norm_groups"]), "eps": self.eps})
+            "state": int(mixer["state"]), "groups": int(mixer.get("groups", 1)), "taps": int(mixer["conv"]),
+            "norm_groups": int(mixer.get("norm_groups", 1)), "eps": self.eps})
 
     def _mixer(self, kind: str, mixer: Mapping[str, Any]) -> PartSpec:
         if kind == "attention":
@@ -229,7 +233,8 @@ class KufulixConfig:
         return PartSpec("parallel_mixers", {
             "left": self._attention(mixer["left"], windowed=True),
             "right": self._state_space(mixer["right"]),
-            "left_scale": float(mixer["left_scale"]), "right_scale": float(mixer["right_scale"])})
+            "left_scale": float(mixer.get("left_scale", 1.0)),
+            "right_scale": float(mixer.get("right_scale", 1.0))})
 
     def _feed_forward(self, mlp: Optional[Mapping[str, Any]]) -> Optional[PartSpec]:
         if mlp is None:

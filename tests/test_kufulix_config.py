@@ -77,8 +77,25 @@ def test_refusals_name_the_place():
     assert "weights_of" in refused(lambda d: d["layers"][2].update(weights_of=2))
     assert "weights_of" in refused(lambda d: d["layers"][4].update(weights_of=2))     # names a layer without tensors
     assert "another layer" in refused(lambda d: d["layers"][2].update(weights_of=1))
-    assert "left_scale" in refused(lambda d: d["layers"][0]["mixer"].pop("left_scale"))
-    assert "mask" in refused(lambda d: d["layers"][1]["mixer"].pop("mask"))
+    assert "left_scale" in refused(lambda d: d["layers"][0]["mixer"].update(left_scale="wide"))
+    assert "mask" in refused(lambda d: d["layers"][1]["mixer"].update(mask=7))
+
+
+def test_what_may_be_absent():
+    data = copy.deepcopy(km.CONFIGS["window"])
+    mixer = data["layers"][0]["mixer"]
+    mixer.pop("left_scale")
+    mixer["left"].pop("mask")
+    mixer["left"].pop("rot")
+    mixer["right"].pop("groups")
+    mixer["right"].pop("norm_groups")
+    data.pop("logit_softcap")
+    spec = config_from_dict(data).build_spec()
+    part = spec.layers[0].mixer
+    assert part.params["left_scale"] == 1.0 and part.params["right_scale"] == 1.5
+    left, right = part.params["left"].params, part.params["right"].params
+    assert left["window"] == 0 and left["chunk"] == 0 and left["position"].kind == "none"
+    assert right["groups"] == 1 and right["norm_groups"] == 1 and spec.logit_softcap == 0.0
 
 
 def test_frequency_table_against_the_formula():
